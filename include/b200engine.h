@@ -174,6 +174,39 @@ int b200_engine_load_safetensors(b200_engine* e, const char* path);
 /* JSON listing of the tensors of a checkpoint (dir, shard index or single file); returns the length needed. */
 int64_t b200_safetensors_list(const char* path, char* buf, size_t cap);
 
+/* ------------------------------------------------------------------ model directories of any registered design
+ * <dir>/config.json names the design: HF "model_type": "llama" is the built-in Llama kernel sequence; an "architecture"
+ * string selects a registered design (csrc/model_registry.cc; "Nomanex": parallel layers of gated linear attention or
+ * windowed latent attention with dense or mixture-of-experts feed-forwards on an fp32 residual stream).  The backend pod
+ * the reference starts picks its model class from the same file (internal/modelcontroller/engine_vllm.go:34-41). */
+enum { B200_DTYPE_BF16 = 0, B200_DTYPE_F32 = 1 };
+enum { B200_CREATE_RANDOM_WEIGHTS = 1 };   /* no model.safetensors in <dir>: seeded random weights (cfg->seed) */
+/* limits: device, max_model_len, max_num_seqs, max_batched_tokens, num_kv_blocks / kv_fraction, manual_step, record_steps,
+ * eos_token_id, seed are taken from it, the architecture fields from the directory.  dtype: storage and arithmetic of
+ * matrices and activations; B200_DTYPE_F32 runs everything in true 32-bit and exists for registered designs only. */
+int b200_engine_create_from_dir(const char* dir, const b200_config* limits, int32_t dtype, int32_t flags, b200_engine** out);
+
+/* Fed sequences (manual_step engines): the caller supplies every token, step by step, and reads logits — replaying a
+ * recorded schedule, scoring, teacher forcing.  A fed step runs exactly the listed tokens of the listed sequences as one
+ * batch through the engine's own page / slot bookkeeping, packing and kernels; entries of one token are decode work,
+ * longer ones prefill portions.  Calls must come from the thread that steps the engine. */
+typedef struct {
+  uint64_t req_id;         /* from b200_feed_open */
+  const int32_t* tokens;   /* the sequence's next n_tokens tokens */
+  int32_t n_tokens;
+  const int32_t* want;     /* offsets among these tokens whose logits are wanted (may be NULL when n_want == 0) */
+  int32_t n_want;
+} b200_feed_entry;
+int b200_feed_open(b200_engine* e, uint64_t* req_id);
+/* logits_out: fp32 [sum of n_want, vocab] in the order of the entries and of their want lists. */
+int b200_feed_step(b200_engine* e, const b200_feed_entry* entries, int32_t n, float* logits_out, int64_t cap_floats);
+/* Gives the sequence's pages and state slot back to the pools. */
+int b200_feed_close(b200_engine* e, uint64_t req_id);
+/* Debug (registered designs): with on != 0 every later step appends the fp32 residual stream [tokens, width] after each
+ * layer run to a host buffer; read returns the number of floats held (and copies them when cap_floats suffices). */
+int b200_engine_debug_residuals(b200_engine* e, int32_t on);
+int64_t b200_engine_read_residuals(b200_engine* e, float* out, int64_t cap_floats);
+
 /* ------------------------------------------------------------------ router
  * Port of internal/loadbalancer group / CHWBL / LeastLoad (group.go:25-150, balance_chwbl.go:14-162,
  * balance_least_load.go:3-23).  "Endpoints" are GPU replicas; address strings are kept so the

@@ -25,6 +25,13 @@ SOURCES = [
     "attention.cu",
     "attention_tc.cu",
     "elementwise.cu",
+    "linear.cu",
+    "norm_act.cu",
+    "gla.cu",
+    "latent_attention.cu",
+    "moe.cu",
+    "nomanex.cu",
+    "model_registry.cc",
     "abi_ops.cu",
     "engine.cu",
     "router.cc",

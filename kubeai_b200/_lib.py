@@ -41,6 +41,11 @@ class Gemm3Args(C.Structure):
                 ("argmax_out", C.c_void_p), ("n_valid", C.c_int32), ("normed_out", C.c_void_p), ("norm_w_out", C.c_void_p)]
 
 
+class FeedEntry(C.Structure):
+    _fields_ = [("req_id", C.c_uint64), ("tokens", C.POINTER(C.c_int32)), ("n_tokens", C.c_int32),
+                ("want", C.POINTER(C.c_int32)), ("n_want", C.c_int32)]
+
+
 class Sampling(C.Structure):
     _fields_ = [("max_tokens", C.c_int32), ("temperature", C.c_float), ("ignore_eos", C.c_int32),
                 ("num_stop_ids", C.c_int32), ("stop_ids", C.POINTER(C.c_int32))]
@@ -138,6 +143,12 @@ SYMBOLS = {
     "b200_config_from_hf": (C.c_int, [C.c_char_p, C.POINTER(Config)]),
     "b200_engine_load_safetensors": (C.c_int, [_vp, C.c_char_p]),
     "b200_safetensors_list": (C.c_int64, [C.c_char_p, C.c_char_p, C.c_size_t]),
+    "b200_engine_create_from_dir": (C.c_int, [C.c_char_p, C.POINTER(Config), _i32, _i32, C.POINTER(_vp)]),
+    "b200_feed_open": (C.c_int, [_vp, C.POINTER(_u64)]),
+    "b200_feed_step": (C.c_int, [_vp, C.POINTER(FeedEntry), _i32, C.POINTER(C.c_float), _i64]),
+    "b200_feed_close": (C.c_int, [_vp, _u64]),
+    "b200_engine_debug_residuals": (C.c_int, [_vp, _i32]),
+    "b200_engine_read_residuals": (C.c_int64, [_vp, C.POINTER(C.c_float), _i64]),
     "b200_router_create": (C.c_int, [_i32, C.POINTER(_vp)]),
     "b200_router_destroy": (None, [_vp]),
     "b200_router_set_endpoints": (C.c_int, [_vp, C.POINTER(C.c_char_p), C.POINTER(C.c_char_p),

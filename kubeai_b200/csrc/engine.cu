@@ -36,6 +36,7 @@
 #include "epi_pass.cuh"
 #include "chain.h"
 #include "kernels.h"
+#include "model.h"
 #include "hostutil.h"
 #include "xxh64.h"
 
@@ -178,6 +179,8 @@ struct Seq {
   std::atomic<int> n_cached{-1};  // prefix-hit tokens at first admission
   bool admitted = false;
   bool leaving = false;  // finished in the step being completed: swept out of the running list
+  int state_slot = -1;   // recurrent-state slot (models with per-sequence state), held while the sequence holds pages
+  bool fed = false;      // tokens come from the caller step by step (b200_feed_*); nothing is sampled into toks
   // shared with API threads: guarded by m (one lock per request, so a step's 128 wake-ups do not convoy on one mutex)
   std::mutex m;
   std::condition_variable cv;
@@ -208,6 +211,7 @@ struct Pub {
 struct StepMeta {
   int T = 0, nd = 0, np = 0, S = 0, nseq = 0;
   int off_ids = 0, off_pos = 0, off_slots = 0, off_rows = 0, off_dwork = 0, off_pwork = 0, off_btab = 0;
+  int off_prev = 0, off_seqtok = 0, off_seqs = 0;   // model engines: previous token and sequence of every token, per-sequence table
   int words = 0;
   int64_t kv_tokens = 0;
   int out_tokens = 0;  // sampled rows that produce a generated token
@@ -223,6 +227,13 @@ struct XMaps {
 // ------------------------------------------------------------------ engine
 struct Engine {
   b200_config cfg;
+  // a design other than the built-in Llama sequence (model.h): it owns weights, caches and states; the engine keeps
+  // scheduling, pages, slots, packing and sampling
+  std::unique_ptr<Model> model;
+  std::vector<int> free_slots;
+  float* feed_logits_host = nullptr;   // pinned staging of b200_feed_step's logits
+  size_t feed_logits_cap = 0;
+  std::vector<float> residual_dump;
   int L, H, Hq, Hkv, I, V, QKV;
   int Tcap, Scap, max_blocks_per_seq;
   cudaStream_t stream = nullptr;
@@ -309,6 +320,11 @@ struct Engine {
 
   ~Engine();
   int init(const b200_config& c);
+  int init_model(const b200_config& c, std::unique_ptr<Model> mdl);
+  int alloc_step_ring();
+  int forward_model(const StepMeta& m, int32_t* dbuf, float* host_logits);
+  int pack(InFlight* f, const std::vector<std::vector<int>>* want, StepMeta* mp);
+  int feed_step(const b200_feed_entry* entries, int n, float* logits_out, int64_t cap_floats);
   int alloc_all();
   int forward(const StepMeta& m, int32_t* dbuf, bool all_logits, bf16* logits_out);
   int forward_fused(const StepMeta& m, int32_t* dbuf);
@@ -394,6 +410,8 @@ Engine::~Engine() {
   for (auto p : stage_dev)
     if (p) cudaFree(p);
   if (stage_host) cudaFreeHost(stage_host);
+  if (feed_logits_host) cudaFreeHost(feed_logits_host);
+  model.reset();   // frees the model's device memory while the context is current
   if (sampled_host) cudaFreeHost(sampled_host);
   if (ev0) cudaEventDestroy(ev0);
   if (ev1) cudaEventDestroy(ev1);
@@ -596,15 +614,87 @@ int Engine::alloc_all() {
   CK(cudaMemsetAsync(kv, 0, kv_layer_elems * 2 * L, stream));
   pool.init(nblocks, cfg.enable_prefix_caching != 0);
 
-  // ---- step input ring
+  if (int rc = alloc_step_ring()) return rc;
+  CK(cudaStreamSynchronize(stream));
+  return 0;
+}
+
+int Engine::alloc_step_ring() {
   max_blocks_per_seq = (cfg.max_model_len + kPage - 1) / kPage;
-  step_words_cap = 3 * Tcap + Scap + 4 * Scap + 4 * (Tcap / 16 + Scap + 1) + Scap * max_blocks_per_seq + 64;
+  // ids, positions, slots, previous ids, sequence of each token, wanted rows (a fed step may want every row), the
+  // per-sequence table, attention work lists, block tables
+  step_words_cap = 6 * Tcap + 9 * Scap + 4 * (Tcap / 16 + Scap + 1) + Scap * max_blocks_per_seq + 64;
   ring_n = std::max(1, cfg.record_steps) + 1;  // last slot = scratch for unrecorded steps
   CK(cudaMallocHost(&stage_host, static_cast<size_t>(step_words_cap) * 4));
   stage_dev.assign(ring_n, nullptr);
   ring_meta.assign(ring_n, StepMeta());
   for (int i = 0; i < ring_n; ++i) CK(cudaMalloc(&stage_dev[i], static_cast<size_t>(step_words_cap) * 4));
+  return 0;
+}
+
+// An engine around a registered design: the model allocates its own weights, activations, per-layer caches (for the
+// pool's pages) and recurrent states (one slot per live sequence); the engine sizes the pool and keeps everything else.
+int Engine::init_model(const b200_config& c, std::unique_ptr<Model> mdl) {
+  cfg = c;
+  model = std::move(mdl);
+  L = H = Hq = Hkv = I = QKV = 0;
+  V = model->vocab();
+  cfg.vocab = V;
+  if (c.max_model_len < 16 || c.max_num_seqs < 1 || c.max_batched_tokens < 16) {
+    set_error("unsupported limits (max_model_len >= 16, max_num_seqs >= 1, max_batched_tokens >= 16)");
+    return B200_ERR_INVALID;
+  }
+  Tcap = (c.max_batched_tokens + 15) / 16 * 16;
+  Scap = c.max_num_seqs;
+  memset(&stats, 0, sizeof(stats));
+  CK(cudaSetDevice(c.device));
+  CK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c.device));
+  CK(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  CK(cudaEventCreate(&ev0));
+  CK(cudaEventCreate(&ev1));
+  const size_t per_block = model->cache_bytes_per_block(kPage);
+  int64_t nblocks = cfg.num_kv_blocks;
+  if (nblocks <= 0) {
+    size_t fr = 0, tot = 0;
+    CK(cudaMemGetInfo(&fr, &tot));
+    const float frac = cfg.kv_fraction > 0 ? cfg.kv_fraction : 0.85f;
+    // weights and activations are allocated after the pool is sized: leave them half of what is free
+    nblocks = per_block ? static_cast<int64_t>(static_cast<double>(fr) * frac * 0.5 / static_cast<double>(per_block)) : 0;
+    nblocks = std::min<int64_t>(nblocks, static_cast<int64_t>(Scap) * ((cfg.max_model_len + kPage - 1) / kPage));
+  }
+  const int64_t need_blocks = (static_cast<int64_t>(cfg.max_model_len) + kPage - 1) / kPage;
+  if (nblocks < need_blocks) {
+    set_error("cache pool too small: %lld blocks, one max_model_len=%d sequence needs %lld", static_cast<long long>(nblocks), cfg.max_model_len,
+              static_cast<long long>(need_blocks));
+    return B200_ERR_OOM;
+  }
+  ModelEnv env;
+  env.stream = stream; env.device = c.device; env.sms = sms; env.Tcap = Tcap; env.max_model_len = cfg.max_model_len;
+  env.page = kPage; env.num_blocks = nblocks; env.num_slots = Scap;
+  if (int rc = model->init(env)) return rc == -3 ? B200_ERR_OOM : (rc == -1 ? B200_ERR_INVALID : B200_ERR_CUDA);
+  // pages of a sequence with recurrent state cannot be shared by prefix: the state after the prefix is not in them
+  pool.init(nblocks, cfg.enable_prefix_caching != 0 && model->state_bytes_per_slot() == 0);
+  free_slots.clear();
+  for (int i = Scap - 1; i >= 0; --i) free_slots.push_back(i);
+  for (auto& kv : model->tensors) tensors[kv.first] = {kv.second.ptr, kv.second.bytes};
+  CK(cudaMalloc(&sampled, static_cast<size_t>(std::max(Scap, Tcap)) * 4));
+  CK(cudaMallocHost(&sampled_host, static_cast<size_t>(Scap) * 4));
+  if (int rc = alloc_step_ring()) return rc;
   CK(cudaStreamSynchronize(stream));
+  stats.kv_blocks_total = pool.total();
+  stats.kv_blocks_free = pool.free_count();
+  if (!c.manual_step) worker = std::thread([this] { loop(); });
+  return 0;
+}
+
+int Engine::forward_model(const StepMeta& m, int32_t* dbuf, float* host_logits) {
+  StepBatch b;
+  b.T = m.T; b.nseq = m.nseq; b.S = m.S;
+  b.ids = dbuf + m.off_ids; b.prev_ids = dbuf + m.off_prev; b.pos = dbuf + m.off_pos; b.slots = dbuf + m.off_slots;
+  b.rows = dbuf + m.off_rows; b.seq_of_tok = dbuf + m.off_seqtok; b.seqs = dbuf + m.off_seqs; b.btab = dbuf + m.off_btab;
+  b.max_blocks = max_blocks_per_seq;
+  last_S = m.S;
+  if (int rc = model->forward(b, sampled, host_logits, &stats.kernel_launches)) return rc == -1 ? B200_ERR_INVALID : B200_ERR_CUDA;
   return 0;
 }
 
@@ -644,6 +734,7 @@ int Engine::init(const b200_config& c) {
 
 // ------------------------------------------------------------------ forward pass (fixed kernel sequence)
 int Engine::forward(const StepMeta& m, int32_t* dbuf, bool all_logits, bf16* logits_out) {
+  if (model) return forward_model(m, dbuf, nullptr);
   const int T = m.T;
   const int* ids = dbuf + m.off_ids;
   const int* pos = dbuf + m.off_pos;
@@ -1010,9 +1101,12 @@ int Engine::forward_chain(const StepMeta& m, int32_t* dbuf) {
 
 // ------------------------------------------------------------------ scheduler helpers
 bool Engine::ensure_blocks(Seq& s, int upto) {
+  const bool wants_slot = model && model->state_bytes_per_slot() > 0 && s.state_slot < 0;
+  if (wants_slot && free_slots.empty()) return false;
   const int need = (upto + kPage - 1) / kPage - static_cast<int>(s.blocks.size());
+  if (need > 0 && pool.free_count() < need) return false;
+  if (wants_slot) { s.state_slot = free_slots.back(); free_slots.pop_back(); }
   if (need <= 0) return true;
-  if (pool.free_count() < need) return false;
   for (int i = 0; i < need; ++i) s.blocks.push_back(pool.alloc());
   return true;
 }
@@ -1021,6 +1115,8 @@ void Engine::release_blocks(Seq& s) {
   // tail blocks go to the front of the LRU free queue order first (vLLM frees in reverse)
   for (auto it = s.blocks.rbegin(); it != s.blocks.rend(); ++it) pool.unref(*it);
   s.blocks.clear();
+  // the slot's contents are not cleared: a sequence that starts at position 0 ignores what its slot held
+  if (s.state_slot >= 0) { free_slots.push_back(s.state_slot); s.state_slot = -1; }
   s.n_computed = 0;
   s.n_published = 0;
   s.chain_uid = 0;
@@ -1074,6 +1170,97 @@ void Engine::admit_prefix(Seq& s) {
     stats.cached_prompt_tokens += s.n_computed;
     stats.prompt_tokens += s.n_prompt;
   }
+}
+
+// Pack the device inputs of a step that runs f->sched[i].n tokens of each sequence, from its n_computed on, into the pinned
+// staging buffer.  want (optional): per sequence, the offsets among its n tokens whose logits are wanted; without it the last
+// token of every sequence that reaches the end of its tokens is a sampling row.
+int Engine::pack(InFlight* f, const std::vector<std::vector<int>>* want, StepMeta* mp) {
+  const std::vector<Sched>& sched = f->sched;
+  StepMeta m;
+  m.nseq = static_cast<int>(sched.size());
+  for (auto& sc : sched) m.T += sc.n;
+  dwork_.clear();
+  pwork_.clear();
+  rows_.clear();
+  int32_t* h = stage_host;
+  m.off_ids = 0; m.off_pos = m.T; m.off_slots = 2 * m.T;
+  int tok = 0;
+  f->ndec_seq = f->npre_seq = 0;
+  for (int si = 0; si < m.nseq; ++si) {
+    Seq& s = *sched[si].s;
+    const int n = sched[si].n, p0 = s.n_computed;
+    for (int j = 0; j < n; ++j) {
+      const int p = p0 + j;
+      h[m.off_ids + tok + j] = s.toks[p];
+      h[m.off_pos + tok + j] = p;
+      h[m.off_slots + tok + j] = s.blocks[p / kPage] * kPage + (p % kPage);
+    }
+    if (n == 1) {
+      dwork_.push_back({tok, 1, p0, si});
+      m.kv_tokens += p0 + 1;
+      ++f->ndec_seq;
+    } else {
+      const int qb = prefill_attn_query_block();   // 64 query tokens per work item on the tensor-core kernel
+      for (int j = 0; j < n; j += qb) pwork_.push_back({tok + j, std::min(qb, n - j), p0 + j, si});
+      m.kv_tokens += p0 + n;  // unique K/V tokens this sequence streams from HBM (query tiles re-read them from L2)
+      ++f->npre_seq;
+    }
+    if (want) for (int off : (*want)[si]) rows_.push_back(tok + off);
+    else if (p0 + n == static_cast<int>(s.toks.size())) rows_.push_back(tok + n - 1);
+    tok += n;
+  }
+  // longest-context work first: CTAs are dispatched in blockIdx order, so the tail of the attention grid is made of
+  // the shortest sequences (LPT scheduling) instead of whatever happened to be last
+  auto longer = [](const AttnWork& a, const AttnWork& b) { return a.q_pos0 + a.q_count > b.q_pos0 + b.q_count; };
+  std::stable_sort(dwork_.begin(), dwork_.end(), longer);
+  std::stable_sort(pwork_.begin(), pwork_.end(), longer);
+  m.nd = static_cast<int>(dwork_.size());
+  m.dmax_ctx = m.nd ? dwork_[0].q_pos0 + 1 : 0;   // sorted longest-first
+  m.np = static_cast<int>(pwork_.size());
+  m.S = static_cast<int>(rows_.size());
+  m.out_tokens = m.S;
+  if (6 * m.T + 9 * m.nseq + 4 * (static_cast<int>(dwork_.size() + pwork_.size()) + 1) + m.nseq * max_blocks_per_seq + 16 > step_words_cap ||
+      (want && m.S > Tcap)) {
+    set_error("step staging overflow (%d tokens, %d sequences)", m.T, m.nseq);
+    return B200_ERR_INVALID;
+  }
+  int w = 3 * m.T;
+  m.off_rows = w; memcpy(h + w, rows_.data(), rows_.size() * 4); w += m.S;
+  w = (w + 3) & ~3;
+  m.off_dwork = w; memcpy(h + w, dwork_.data(), dwork_.size() * 16); w += 4 * m.nd;
+  m.off_pwork = w; memcpy(h + w, pwork_.data(), pwork_.size() * 16); w += 4 * m.np;
+  if (model) {
+    // what a design with a hashed-bigram input, recurrent slots or per-token page lookups needs beside ids / positions / slots
+    m.off_prev = w; m.off_seqtok = w + m.T; w += 2 * m.T;
+    m.off_seqs = w; w += 8 * m.nseq;
+    int t0 = 0;
+    for (int si = 0; si < m.nseq; ++si) {
+      const Seq& s = *sched[si].s;
+      const int n = sched[si].n, p0 = s.n_computed;
+      for (int j = 0; j < n; ++j) {
+        h[m.off_prev + t0 + j] = p0 + j > 0 ? s.toks[p0 + j - 1] : -1;
+        h[m.off_seqtok + t0 + j] = si;
+      }
+      int32_t* q = h + m.off_seqs + 8 * si;
+      q[0] = t0; q[1] = n; q[2] = p0; q[3] = s.state_slot < 0 ? 0 : s.state_slot; q[4] = q[5] = q[6] = q[7] = 0;
+      t0 += n;
+    }
+  }
+  m.off_btab = w;
+  for (int si = 0; si < m.nseq; ++si) {
+    Seq& s = *sched[si].s;
+    memcpy(h + w + static_cast<size_t>(si) * max_blocks_per_seq, s.blocks.data(), s.blocks.size() * 4);
+  }
+  w += m.nseq * max_blocks_per_seq;
+  m.words = w;
+  if (w > step_words_cap) {
+    set_error("step staging overflow (%d > %d words)", w, step_words_cap);
+    return B200_ERR_INVALID;
+  }
+
+  *mp = m;
+  return 0;
 }
 
 // ------------------------------------------------------------------ one scheduler iteration + forward
@@ -1160,65 +1347,10 @@ int Engine::launch(InFlight* f, StepMeta* mp) {
   }
   if (sched.empty()) return 0;
 
-  // ---- pack the step's device inputs
   StepMeta m;
-  m.nseq = static_cast<int>(sched.size());
-  for (auto& sc : sched) m.T += sc.n;
-  dwork_.clear();
-  pwork_.clear();
-  rows_.clear();
+  if (int prc = pack(f, nullptr, &m)) return prc;
   int32_t* h = stage_host;
-  m.off_ids = 0; m.off_pos = m.T; m.off_slots = 2 * m.T;
-  int tok = 0;
-  f->ndec_seq = f->npre_seq = 0;
-  for (int si = 0; si < m.nseq; ++si) {
-    Seq& s = *sched[si].s;
-    const int n = sched[si].n, p0 = s.n_computed;
-    for (int j = 0; j < n; ++j) {
-      const int p = p0 + j;
-      h[m.off_ids + tok + j] = s.toks[p];
-      h[m.off_pos + tok + j] = p;
-      h[m.off_slots + tok + j] = s.blocks[p / kPage] * kPage + (p % kPage);
-    }
-    if (n == 1) {
-      dwork_.push_back({tok, 1, p0, si});
-      m.kv_tokens += p0 + 1;
-      ++f->ndec_seq;
-    } else {
-      const int qb = prefill_attn_query_block();   // 64 query tokens per work item on the tensor-core kernel
-      for (int j = 0; j < n; j += qb) pwork_.push_back({tok + j, std::min(qb, n - j), p0 + j, si});
-      m.kv_tokens += p0 + n;  // unique K/V tokens this sequence streams from HBM (query tiles re-read them from L2)
-      ++f->npre_seq;
-    }
-    if (p0 + n == static_cast<int>(s.toks.size())) rows_.push_back(tok + n - 1);
-    tok += n;
-  }
-  // longest-context work first: CTAs are dispatched in blockIdx order, so the tail of the attention grid is made of
-  // the shortest sequences (LPT scheduling) instead of whatever happened to be last
-  auto longer = [](const AttnWork& a, const AttnWork& b) { return a.q_pos0 + a.q_count > b.q_pos0 + b.q_count; };
-  std::stable_sort(dwork_.begin(), dwork_.end(), longer);
-  std::stable_sort(pwork_.begin(), pwork_.end(), longer);
-  m.nd = static_cast<int>(dwork_.size());
-  m.dmax_ctx = m.nd ? dwork_[0].q_pos0 + 1 : 0;   // sorted longest-first
-  m.np = static_cast<int>(pwork_.size());
-  m.S = static_cast<int>(rows_.size());
-  m.out_tokens = m.S;
-  int w = 3 * m.T;
-  m.off_rows = w; memcpy(h + w, rows_.data(), rows_.size() * 4); w += m.S;
-  w = (w + 3) & ~3;
-  m.off_dwork = w; memcpy(h + w, dwork_.data(), dwork_.size() * 16); w += 4 * m.nd;
-  m.off_pwork = w; memcpy(h + w, pwork_.data(), pwork_.size() * 16); w += 4 * m.np;
-  m.off_btab = w;
-  for (int si = 0; si < m.nseq; ++si) {
-    Seq& s = *sched[si].s;
-    memcpy(h + w + static_cast<size_t>(si) * max_blocks_per_seq, s.blocks.data(), s.blocks.size() * 4);
-  }
-  w += m.nseq * max_blocks_per_seq;
-  m.words = w;
-  if (w > step_words_cap) {
-    set_error("step staging overflow (%d > %d words)", w, step_words_cap);
-    return B200_ERR_INVALID;
-  }
+  const int w = m.words;
 
   int slot = ring_n - 1;  // scratch
   if (recording && ring_n > 1) {
@@ -1325,6 +1457,91 @@ int Engine::complete(InFlight& f, const StepMeta& m, b200_step_info* info) {
     info->device_us = ms * 1000.0;
   }
   return 1;
+}
+
+// One step whose tokens the caller supplies (b200_feed_step): the listed sequences advance by exactly the given tokens, as
+// one batch, through the same page / slot bookkeeping, packing and forward pass as a scheduled step; nothing is sampled
+// into the sequences.  Logits of the wanted positions go to logits_out in the order of the entries.
+int Engine::feed_step(const b200_feed_entry* entries, int n, float* logits_out, int64_t cap_floats) {
+  InFlight& f = inflight_;
+  f.sched.clear();
+  std::vector<std::vector<int>> want(n);
+  int T = 0;
+  int64_t S = 0;
+  for (int i = 0; i < n; ++i) {
+    const b200_feed_entry& en = entries[i];
+    std::shared_ptr<Seq> s;
+    {
+      std::lock_guard<std::mutex> lk(mu_);
+      auto it = requests.find(en.req_id);
+      if (it != requests.end()) s = it->second;
+    }
+    if (!s || !s->fed) { set_error("feed: request %llu was not opened with b200_feed_open", static_cast<unsigned long long>(en.req_id)); return B200_ERR_NOT_FOUND; }
+    if (en.n_tokens <= 0 || !en.tokens || (en.n_want > 0 && !en.want)) { set_error("feed: an entry needs at least one token"); return B200_ERR_INVALID; }
+    for (auto& sc : f.sched) if (sc.s == s) { set_error("feed: a request appears twice in one step"); return B200_ERR_INVALID; }
+    for (int j = 0; j < en.n_tokens; ++j) if (en.tokens[j] < 0 || en.tokens[j] >= V) { set_error("feed: token id out of range"); return B200_ERR_INVALID; }
+    for (int j = 0; j < en.n_want; ++j) {
+      if (en.want[j] < 0 || en.want[j] >= en.n_tokens) { set_error("feed: wanted position outside the entry's tokens"); return B200_ERR_INVALID; }
+      want[i].push_back(en.want[j]);
+    }
+    if (static_cast<int64_t>(s->toks.size()) + en.n_tokens > cfg.max_model_len) { set_error("feed: sequence would exceed max_model_len %d", cfg.max_model_len); return B200_ERR_INVALID; }
+    T += en.n_tokens;
+    S += en.n_want;
+    f.sched.push_back({s, en.n_tokens});
+  }
+  if (n > Scap || T > Tcap || T > cfg.max_batched_tokens) { set_error("feed: %d tokens of %d sequences exceed the engine's limits (%d, %d)", T, n, cfg.max_batched_tokens, Scap); return B200_ERR_INVALID; }
+  if (S * V > cap_floats || (S > 0 && !logits_out)) { set_error("feed: logits buffer too small"); return B200_ERR_INVALID; }
+  if (!model && S > Scap) { set_error("feed: at most max_num_seqs = %d wanted rows per step on the built-in model", Scap); return B200_ERR_INVALID; }
+  for (int i = 0; i < n; ++i) {
+    Seq& s = *f.sched[i].s;
+    if (!ensure_blocks(s, s.n_computed + f.sched[i].n)) { set_error("feed: out of cache pages or state slots"); return B200_ERR_OOM; }
+  }
+  for (int i = 0; i < n; ++i) {
+    Seq& s = *f.sched[i].s;
+    s.toks.insert(s.toks.end(), entries[i].tokens, entries[i].tokens + entries[i].n_tokens);
+  }
+  StepMeta m;
+  int rc = pack(&f, &want, &m);
+  if (!rc) {
+    int32_t* dbuf = stage_dev[ring_n - 1];
+    CK(cudaMemcpyAsync(dbuf, stage_host, static_cast<size_t>(m.words) * 4, cudaMemcpyHostToDevice, stream));
+    CK(cudaEventRecord(ev0, stream));
+    if (model) rc = forward_model(m, dbuf, logits_out);
+    else {
+      const bool keep = keep_logits;
+      keep_logits = true;
+      rc = forward(m, dbuf, false, nullptr);
+      keep_logits = keep;
+      if (!rc && m.S) {
+        std::vector<bf16> tmp(static_cast<size_t>(m.S) * V);
+        CK(cudaMemcpyAsync(tmp.data(), logits, tmp.size() * 2, cudaMemcpyDeviceToHost, stream));
+        CK(cudaStreamSynchronize(stream));
+        for (size_t i = 0; i < tmp.size(); ++i) logits_out[i] = __bfloat162float(tmp[i]);
+      }
+    }
+    if (!rc) {
+      CK(cudaEventRecord(ev1, stream));
+      CK(cudaStreamSynchronize(stream));
+    }
+  }
+  if (rc) {
+    for (int i = 0; i < n; ++i) f.sched[i].s->toks.resize(f.sched[i].s->toks.size() - entries[i].n_tokens);
+    return rc;
+  }
+  for (int i = 0; i < n; ++i) f.sched[i].s->n_computed += f.sched[i].n;
+  float ms = 0.f;
+  cudaEventElapsedTime(&ms, ev0, ev1);
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    ++stats.steps;
+    stats.last_step_device_us = ms * 1000.0;
+    stats.total_device_us += ms * 1000.0;
+    stats.last_step_tokens = m.T;
+    stats.h2d_bytes += static_cast<int64_t>(m.words) * 4;
+    stats.d2h_bytes += S * V * 4;
+    stats.kv_blocks_free = pool.free_count();
+  }
+  return 0;
 }
 
 // One synchronous iteration (tests, debugging): results are visible to poll() when it returns.
@@ -1812,6 +2029,76 @@ int b200_engine_forward_logits(b200_engine* e, const int32_t* ids, int32_t n, vo
   cudaFree(dl);
   for (auto it = s.blocks.rbegin(); it != s.blocks.rend(); ++it) g.pool.unref(*it);
   return rc;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------- engines around a registered design, fed steps
+int b200::engine_create_with_model(const b200_config* cfg, std::unique_ptr<b200::Model> mdl, b200_engine** out) {
+  if (!cfg || !out || !mdl) { set_error("null argument"); return B200_ERR_INVALID; }
+  if (int rc = require_device()) return rc;
+  b200_engine* e = new (std::nothrow) b200_engine();
+  if (!e) { set_error("host OOM"); return B200_ERR_OOM; }
+  int rc = e->impl.init_model(*cfg, std::move(mdl));
+  if (rc) { delete e; return rc; }
+  *out = e;
+  return 0;
+}
+
+b200::Model* b200::engine_model(b200_engine* e) { return e ? e->impl.model.get() : nullptr; }
+
+extern "C" {
+
+int b200_feed_open(b200_engine* e, uint64_t* req_id) {
+  if (!e || !req_id) { set_error("null argument"); return B200_ERR_INVALID; }
+  Engine& g = e->impl;
+  if (!g.cfg.manual_step) { set_error("fed sequences need manual_step"); return B200_ERR_INVALID; }
+  auto s = std::make_shared<Seq>();
+  s->fed = true;
+  std::lock_guard<std::mutex> lk(g.mu_);
+  if (g.fatal) { set_error("engine is in a failed state"); return B200_ERR_CUDA; }
+  s->id = g.next_id++;
+  g.requests[s->id] = s;
+  *req_id = s->id;
+  return 0;
+}
+
+int b200_feed_step(b200_engine* e, const b200_feed_entry* entries, int32_t n, float* logits_out, int64_t cap_floats) {
+  if (!e || !entries || n <= 0) { set_error("b200_feed_step: bad arguments"); return B200_ERR_INVALID; }
+  if (!e->impl.cfg.manual_step) { set_error("fed sequences need manual_step"); return B200_ERR_INVALID; }
+  cudaSetDevice(e->impl.cfg.device);
+  return e->impl.feed_step(entries, n, logits_out, cap_floats);
+}
+
+int b200_feed_close(b200_engine* e, uint64_t req_id) {
+  if (!e) { set_error("null engine"); return B200_ERR_INVALID; }
+  Engine& g = e->impl;
+  std::shared_ptr<Seq> s;
+  {
+    std::lock_guard<std::mutex> lk(g.mu_);
+    auto it = g.requests.find(req_id);
+    if (it == g.requests.end() || !it->second->fed) { set_error("unknown fed request"); return B200_ERR_NOT_FOUND; }
+    s = it->second;
+    g.requests.erase(it);
+  }
+  g.release_blocks(*s);
+  std::lock_guard<std::mutex> lk(g.mu_);
+  g.stats.kv_blocks_free = g.pool.free_count();
+  return 0;
+}
+
+int b200_engine_debug_residuals(b200_engine* e, int32_t on) {
+  if (!e || !e->impl.model) { set_error("residual capture needs an engine around a registered design"); return B200_ERR_INVALID; }
+  e->impl.residual_dump.clear();
+  e->impl.model->residual_sink = on ? &e->impl.residual_dump : nullptr;
+  return 0;
+}
+
+int64_t b200_engine_read_residuals(b200_engine* e, float* out, int64_t cap_floats) {
+  if (!e) { set_error("null engine"); return B200_ERR_INVALID; }
+  const int64_t n = static_cast<int64_t>(e->impl.residual_dump.size());
+  if (out && cap_floats >= n) memcpy(out, e->impl.residual_dump.data(), static_cast<size_t>(n) * sizeof(float));
+  return n;
 }
 
 }  // extern "C"

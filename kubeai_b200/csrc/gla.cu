@@ -1,0 +1,138 @@
+// Gated linear attention (mixers.h GlaArgs): a recurrent mixer whose per-head state S [dim, vdim] is decayed per key
+// channel and updated with an outer product, S_t = diag(alpha_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t.
+//
+// The scan is sequential in the token and exact: the same fp32 operations in the same order whether a sequence's tokens
+// arrive in one step or one at a time, so chunked prefill and decode agree bit for bit.  Parallelism comes from the
+// independent columns of S: a thread owns one value column j and a slice of the key rows, keeps that slice of the state in
+// registers for the whole step, and P = 1, 2, 4 ... row slices are reduced with shuffles.  q, k and the decay of a group
+// of tokens are staged in shared memory once per CTA; the decay is alpha = exp(inv_tau * logsigmoid(z + bias)) in fp32.
+// The state lives in HBM between steps ([slot][head][dim][vdim] fp32) and is read and written once per step.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "mixers.h"
+
+namespace b200 {
+namespace {
+
+typedef __nv_bfloat16 bf16;
+__device__ __forceinline__ float ldf(const float* p) { return *p; }
+__device__ __forceinline__ float ldf(const bf16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stf(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+constexpr int kRows = 32;      // key rows of the state held by one thread
+constexpr int kGroup = 8;      // tokens staged per shared-memory round
+constexpr int kThreads = 128;
+
+// grid: (ceil(vdim / (kThreads / P)), heads, nseq); P = row slices per column (a power of two, P * kRows >= dim)
+template <typename T>
+__global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, int rows_per_part) {
+  extern __shared__ float sm[];   // [kGroup][3][dim]: q (scaled), k, alpha
+  const int seq = blockIdx.z, head = blockIdx.y;
+  const int tok0 = a.seqs[seq * 8 + 0], n = a.seqs[seq * 8 + 1], pos0 = a.seqs[seq * 8 + 2], slot = a.seqs[seq * 8 + 3];
+  const int D = a.dim, Dv = a.vdim;
+  const int part = threadIdx.x % P, jj = threadIdx.x / P;
+  const int cols = kThreads / P;
+  const int j = blockIdx.x * cols + jj;
+  const bool live = j < Dv;
+  const int i0 = part * rows_per_part;
+  const T* base = static_cast<const T*>(a.qkv);
+  float* Sg = a.states + ((static_cast<long long>(slot) * a.heads + head) * D) * Dv;
+  float S[kRows];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) {
+    const int i = i0 + r;
+    S[r] = (live && r < rows_per_part && i < D && pos0 > 0) ? Sg[static_cast<long long>(i) * Dv + j] : 0.f;
+  }
+  for (int g0 = 0; g0 < n; g0 += kGroup) {
+    const int gn = min(kGroup, n - g0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < gn * D; e += kThreads) {
+      const int tt = e / D, i = e - tt * D;
+      const long long row = static_cast<long long>(tok0 + g0 + tt);
+      const T* rp = base + row * a.ld;
+      const int c = head * D + i;
+      const float z = a.z[row * (a.heads * D) + c] + a.z_bias[c];
+      // log sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
+      const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+      float* s3 = sm + (tt * 3) * D;
+      s3[i] = ldf(rp + a.q_off + c) * a.q_scale;
+      s3[D + i] = ldf(rp + a.k_off + c);
+      s3[2 * D + i] = expf(ls * a.inv_tau);
+    }
+    __syncthreads();
+    for (int tt = 0; tt < gn; ++tt) {
+      const long long row = static_cast<long long>(tok0 + g0 + tt);
+      const float v = live ? ldf(base + row * a.ld + a.v_off + head * Dv + j) : 0.f;
+      const float* q = sm + (tt * 3) * D + i0;
+      const float* k = q + D;
+      const float* al = k + D;
+      float o = 0.f;
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        if (r < rows_per_part && i0 + r < D) {
+          S[r] = fmaf(al[r], S[r], k[r] * v);
+          o = fmaf(S[r], q[r], o);
+        }
+      }
+      for (int w = 1; w < P; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+      if (live && part == 0) a.o[row * (a.heads * Dv) + head * Dv + j] = o;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      const int i = i0 + r;
+      if (r < rows_per_part && i < D) Sg[static_cast<long long>(i) * Dv + j] = S[r];
+    }
+  }
+}
+
+// one warp per (token, head): unit RMS over vdim, weight, SiLU gate
+template <typename T>
+__global__ void gla_out_gate_kernel(const float* o, const T* g, int ldg, const float* w, float eps, T* y, int ldy, int heads, int vdim, long long pairs) {
+  const long long p = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (p >= pairs) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = p / heads;
+  const int h = static_cast<int>(p - t * heads);
+  const float* op = o + p * vdim;
+  float ss = 0.f;
+  for (int i = lane; i < vdim; i += 32) ss = fmaf(op[i], op[i], ss);
+  for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+  const float inv = 1.0f / sqrtf(ss / static_cast<float>(vdim) + eps);
+  for (int i = lane; i < vdim; i += 32) {
+    const float gv = ldf(g + t * ldg + h * vdim + i);
+    stf(y + t * ldy + h * vdim + i, op[i] * inv * w[i] * (gv / (1.0f + expf(-gv))));
+  }
+}
+
+}  // namespace
+
+int gla_scan(const GlaArgs& a, cudaStream_t st) {
+  if (a.nseq <= 0) return 0;
+  if (a.dim < 1 || a.vdim < 1 || a.heads < 1) return -1;
+  int P = 1;
+  while (P * kRows < a.dim) P <<= 1;
+  if (P > 32) return -1;   // dim <= 1024
+  const int rows_per_part = (a.dim + P - 1) / P;
+  const int cols = kThreads / P;
+  dim3 grid((a.vdim + cols - 1) / cols, a.heads, a.nseq);
+  const size_t smem = static_cast<size_t>(kGroup) * 3 * a.dim * sizeof(float);
+  if (smem > 48 * 1024) return -1;
+  if (a.t == DT_BF16) gla_scan_kernel<bf16><<<grid, kThreads, smem, st>>>(a, P, rows_per_part);
+  else gla_scan_kernel<float><<<grid, kThreads, smem, st>>>(a, P, rows_per_part);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int gla_out_gate(const float* o, const void* g, int ldg, const float* w, float eps, void* y, int ldy, DType t, int T, int heads, int vdim, cudaStream_t st) {
+  const long long pairs = static_cast<long long>(T) * heads;
+  if (pairs <= 0) return 0;
+  const unsigned grid = static_cast<unsigned>((pairs + 3) / 4);
+  if (t == DT_BF16) gla_out_gate_kernel<bf16><<<grid, 128, 0, st>>>(o, static_cast<const bf16*>(g), ldg, w, eps, static_cast<bf16*>(y), ldy, heads, vdim, pairs);
+  else gla_out_gate_kernel<float><<<grid, 128, 0, st>>>(o, static_cast<const float*>(g), ldg, w, eps, static_cast<float*>(y), ldy, heads, vdim, pairs);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+}  // namespace b200

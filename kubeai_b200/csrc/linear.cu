@@ -1,0 +1,185 @@
+// Shape-agnostic linear layer: Y = act(X W^T) for any T, N, K, in bf16 or fp32 storage with fp32 accumulation.
+// Three uses share one kernel family (mixers.h LinearArgs): a plain projection, one projection per head inside wider
+// rows (batch index = head), and expert-grouped rows (64-row tiles that each name their weight matrix).  It is the
+// projection path of every shape the tcgen05 GEMMs (gemm2_tcgen05.cu: bf16, K % 8 == 0, bf16 output) do not take:
+// fp32 models, fp32 outputs (router logits, decay pre-activations, latent queries), odd sizes, gathers.
+//
+// Two kernels: a 64 x 64 x 32 shared-memory tile kernel (k ascending, so one output element is accumulated in the same
+// order whatever else is in the batch), and a one-warp-per-output-row kernel for steps of at most 8 rows (decode), which
+// streams each weight row once with 16-byte loads.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "mixers.h"
+
+namespace b200 {
+namespace {
+
+typedef __nv_bfloat16 bf16;
+constexpr int BM = 64, BN = 64, BK = 32;
+
+__device__ __forceinline__ float ld1(const float* p) { return *p; }
+__device__ __forceinline__ float ld1(const bf16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void st1(float* p, float v) { *p = v; }
+__device__ __forceinline__ void st1(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void ld8(const float* p, float* o) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+__device__ __forceinline__ void ld8(const bf16* p, float* o) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    o[2 * i] = __uint_as_float(u[i] << 16);
+    o[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == LIN_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
+  return v;
+}
+
+template <typename TX, typename TW, typename TY>
+__global__ void __launch_bounds__(256) linear_tile_kernel(LinearArgs a) {
+  __shared__ float Xs[BM][BK + 1];
+  __shared__ float Ws[BN][BK + 1];
+  const int tid = threadIdx.x, lane = tid & 31, wrp = tid >> 5;
+  const int row0 = blockIdx.y * BM, col0 = blockIdx.x * BN;
+  const long long b = blockIdx.z;
+  const TX* X = static_cast<const TX*>(a.X) + b * a.xbs;
+  const TW* W = static_cast<const TW*>(a.W) + b * a.wbs;
+  TY* Y = static_cast<TY*>(a.Y) + b * a.ybs;
+  if (a.tile_group) {
+    const int g = a.tile_group[blockIdx.y];
+    if (g < 0) return;
+    W += static_cast<long long>(g) * a.wbs;
+  }
+  // the 8 rows of X and of W this thread stages per k-tile (row = warp + 8 i, column = lane)
+  long long xoff[8], woff[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = wrp + 8 * i;
+    int t = row0 + r;
+    if (t >= a.T) t = -1;
+    else if (a.x_rows) t = a.x_rows[t];
+    xoff[i] = t < 0 ? -1 : static_cast<long long>(t) * a.ldx;
+    const int n = col0 + r;
+    woff[i] = n < a.N ? static_cast<long long>(n) * a.ldw : -1;
+  }
+  const int ty = tid >> 4, tx = tid & 15;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < a.K; k0 += BK) {
+    const int k = k0 + lane;
+    const bool kin = k < a.K;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = wrp + 8 * i;
+      Xs[r][lane] = (kin && xoff[i] >= 0) ? ld1(X + xoff[i] + k) : 0.f;
+      Ws[r][lane] = (kin && woff[i] >= 0) ? ld1(W + woff[i] + k) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float xv[4], wv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { xv[i] = Xs[ty * 4 + i][kk]; wv[i] = Ws[tx * 4 + i][kk]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int t = row0 + ty * 4 + i;
+    if (t >= a.T) continue;
+    if (a.x_rows && a.x_rows[t] < 0) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = col0 + tx * 4 + j;
+      if (n < a.N) st1(Y + static_cast<long long>(t) * a.ldy + n, apply_act(acc[i][j], a.act));
+    }
+  }
+}
+
+// T <= 8 rows: one warp per output column n streams W[n, :] once and keeps the T accumulators in registers.
+template <typename TX, typename TW, typename TY, int VEC>
+__global__ void __launch_bounds__(256) linear_rows_kernel(LinearArgs a) {
+  const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
+  const int n = blockIdx.x * 8 + wrp;
+  if (n >= a.N) return;
+  const long long b = blockIdx.z;
+  const TX* X = static_cast<const TX*>(a.X) + b * a.xbs;
+  const TW* w = static_cast<const TW*>(a.W) + b * a.wbs + static_cast<long long>(n) * a.ldw;
+  TY* Y = static_cast<TY*>(a.Y) + b * a.ybs;
+  float acc[8];
+#pragma unroll
+  for (int t = 0; t < 8; ++t) acc[t] = 0.f;
+  for (int k = lane * VEC; k < a.K; k += 32 * VEC) {
+    float wv[VEC];
+    if constexpr (VEC == 8) ld8(w + k, wv); else wv[0] = ld1(w + k);
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      if (t < a.T) {
+        float xv[VEC];
+        const TX* xp = X + static_cast<long long>(t) * a.ldx + k;
+        if constexpr (VEC == 8) ld8(xp, xv); else xv[0] = ld1(xp);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[t] = fmaf(xv[v], wv[v], acc[t]);
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    if (t < a.T) {
+      float v = acc[t];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) st1(Y + static_cast<long long>(t) * a.ldy + n, apply_act(v, a.act));
+    }
+  }
+}
+
+template <typename TX, typename TW, typename TY>
+int launch_linear(const LinearArgs& a, cudaStream_t st) {
+  const bool few = a.T <= 8 && !a.x_rows && !a.tile_group;
+  if (few) {
+    const size_t ex = sizeof(TX), ew = sizeof(TW);
+    const bool vec = a.K % 8 == 0 && a.ldx % 8 == 0 && a.ldw % 8 == 0 && a.xbs % 8 == 0 && a.wbs % 8 == 0 &&
+                     reinterpret_cast<uintptr_t>(a.X) % (8 * ex > 16 ? 16 : 8 * ex) == 0 && reinterpret_cast<uintptr_t>(a.W) % (8 * ew > 16 ? 16 : 8 * ew) == 0;
+    dim3 grid((a.N + 7) / 8, 1, a.batch);
+    if (vec) linear_rows_kernel<TX, TW, TY, 8><<<grid, 256, 0, st>>>(a);
+    else linear_rows_kernel<TX, TW, TY, 1><<<grid, 256, 0, st>>>(a);
+  } else {
+    dim3 grid((a.N + BN - 1) / BN, (a.T + BM - 1) / BM, a.batch);
+    linear_tile_kernel<TX, TW, TY><<<grid, 256, 0, st>>>(a);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+}  // namespace
+
+int linear(const LinearArgs& a, cudaStream_t st) {
+  if (a.T <= 0 || a.N <= 0) return 0;
+  if (!a.X || !a.W || !a.Y || a.K <= 0 || a.batch < 1) return -1;
+  if (a.tile_group && a.T % BM) return -1;
+  const int key = (a.tx == DT_F32 ? 4 : 0) | (a.tw == DT_F32 ? 2 : 0) | (a.ty == DT_F32 ? 1 : 0);
+  switch (key) {
+    case 0: return launch_linear<bf16, bf16, bf16>(a, st);
+    case 1: return launch_linear<bf16, bf16, float>(a, st);
+    case 2: return launch_linear<bf16, float, bf16>(a, st);
+    case 3: return launch_linear<bf16, float, float>(a, st);
+    case 4: return launch_linear<float, bf16, bf16>(a, st);
+    case 5: return launch_linear<float, bf16, float>(a, st);
+    case 6: return launch_linear<float, float, bf16>(a, st);
+    default: return launch_linear<float, float, float>(a, st);
+  }
+}
+
+}  // namespace b200

@@ -21,6 +21,7 @@
 #include "../../include/b200engine.h"
 #include "errors.h"
 #include "hostutil.h"
+#include "model.h"
 
 namespace b200 {
 namespace {
@@ -214,6 +215,47 @@ int copy_rows(const Checkpoint& ck, const std::string& name, void* dev_base, siz
 }  // namespace
 }  // namespace b200
 
+namespace b200 {
+
+struct CheckpointReader::Impl {
+  Checkpoint ck;
+};
+CheckpointReader::CheckpointReader() : impl_(new Impl()) {}
+CheckpointReader::~CheckpointReader() { delete impl_; }
+bool CheckpointReader::open(const std::string& path, std::string* err) { return impl_->ck.open_path(path, err); }
+bool CheckpointReader::has(const std::string& name) const { return impl_->ck.index.count(name) != 0; }
+bool CheckpointReader::shape(const std::string& name, std::vector<int64_t>* out) const {
+  auto it = impl_->ck.index.find(name);
+  if (it == impl_->ck.index.end()) return false;
+  *out = it->second.second->shape;
+  return true;
+}
+bool CheckpointReader::read_f32(const std::string& name, std::vector<float>* out, std::vector<int64_t>* shape, std::string* err) const {
+  auto it = impl_->ck.index.find(name);
+  if (it == impl_->ck.index.end()) { *err = "missing tensor " + name; return false; }
+  const StTensor& t = *it->second.second;
+  const StFile& f = *it->second.first;
+  size_t n = 1;
+  for (auto d : t.shape) n *= static_cast<size_t>(d);
+  const size_t es = t.dtype == "I32" ? 4 : dtype_size(t.dtype);
+  if (!es || t.end - t.begin != n * es) { *err = name + ": unsupported dtype " + t.dtype; return false; }
+  const uint8_t* src = f.map + f.data_off + t.begin;
+  out->resize(n);
+  if (t.dtype == "F32") memcpy(out->data(), src, n * 4);
+  else if (t.dtype == "I32") { const int32_t* p = reinterpret_cast<const int32_t*>(src); for (size_t i = 0; i < n; ++i) (*out)[i] = static_cast<float>(p[i]); }
+  else if (t.dtype == "BF16") {
+    const uint16_t* p = reinterpret_cast<const uint16_t*>(src);
+    for (size_t i = 0; i < n; ++i) { const uint32_t u = static_cast<uint32_t>(p[i]) << 16; memcpy(&(*out)[i], &u, 4); }
+  } else {
+    const uint16_t* p = reinterpret_cast<const uint16_t*>(src);
+    for (size_t i = 0; i < n; ++i) (*out)[i] = f16_to_f32(p[i]);
+  }
+  if (shape) *shape = t.shape;
+  return true;
+}
+
+}  // namespace b200
+
 using namespace b200;
 
 extern "C" {
@@ -356,6 +398,60 @@ int b200_engine_load_safetensors(b200_engine* e, const char* path) {
     LD(hp + "post_attention_layernorm.weight", 0, 1, H);
   }
 #undef LD
+  return 0;
+}
+
+
+// An engine for the model directory `dir`, whatever registered design its config.json names.
+int b200_engine_create_from_dir(const char* dir, const b200_config* limits, int32_t dtype, int32_t flags, b200_engine** out) {
+  if (!dir || !limits || !out) { set_error("null argument"); return B200_ERR_INVALID; }
+  if (dtype != B200_DTYPE_BF16 && dtype != B200_DTYPE_F32) { set_error("unknown dtype %d", dtype); return B200_ERR_INVALID; }
+  std::string txt;
+  if (!read_text(std::string(dir) + "/config.json", &txt)) { set_error("cannot read %s/config.json", dir); return B200_ERR_NOT_FOUND; }
+  JVal root;
+  std::string jerr;
+  if (!JParser(txt.data(), txt.size()).parse(&root, &jerr) || root.type != JVal::Obj) { set_error("config.json: %s", jerr.c_str()); return B200_ERR_INVALID; }
+  const JVal* arch = root.get("architecture");
+  const std::string weights = std::string(dir) + "/model.safetensors";
+  struct stat stt;
+  const bool have_weights = stat(weights.c_str(), &stt) == 0 || stat((std::string(dir) + "/model.safetensors.index.json").c_str(), &stt) == 0;
+  if (!arch || arch->type != JVal::Str) {
+    // HF layout: the built-in Llama sequence (bf16 only)
+    if (dtype != B200_DTYPE_BF16) { set_error("the built-in Llama kernels run in bf16 only"); return B200_ERR_INVALID; }
+    b200_config cfg = *limits;
+    if (int rc = b200_config_from_hf(dir, &cfg)) return rc;
+    if (int rc = b200_engine_create(&cfg, out)) return rc;
+    if (have_weights) {
+      if (int rc = b200_engine_load_safetensors(*out, dir)) { b200_engine_destroy(*out); *out = nullptr; return rc; }
+    } else if (!(flags & B200_CREATE_RANDOM_WEIGHTS)) {
+      b200_engine_destroy(*out); *out = nullptr;
+      set_error("no model.safetensors in %s", dir);
+      return B200_ERR_NOT_FOUND;
+    }
+    return 0;
+  }
+  ModelFactory make = find_model_factory(arch->str);
+  if (!make) { set_error("architecture \"%s\" is not registered (known: %s)", arch->str.c_str(), registered_architectures().c_str()); return B200_ERR_INVALID; }
+  std::string err;
+  std::unique_ptr<Model> mdl = make(root, dtype == B200_DTYPE_F32 ? DT_F32 : DT_BF16, &err);
+  if (!mdl) { set_error("%s: %s", arch->str.c_str(), err.c_str()); return B200_ERR_INVALID; }
+  CheckpointReader ck;
+  if (have_weights) {
+    if (!ck.open(dir, &err)) { set_error("%s", err.c_str()); return B200_ERR_INVALID; }
+    if (mdl->inspect(ck, &err)) { set_error("%s", err.c_str()); return B200_ERR_INVALID; }
+  } else if (!(flags & B200_CREATE_RANDOM_WEIGHTS)) {
+    set_error("no model.safetensors in %s", dir);
+    return B200_ERR_NOT_FOUND;
+  }
+  if (int rc = engine_create_with_model(limits, std::move(mdl), out)) return rc;
+  Model* m = engine_model(*out);
+  int rc = have_weights ? m->load(ck, &err) : m->randomize(limits->seed);
+  if (rc) {
+    if (have_weights) set_error("%s", err.c_str()); else set_error("random weight initialisation failed");
+    b200_engine_destroy(*out);
+    *out = nullptr;
+    return rc == -4 ? B200_ERR_NOT_FOUND : B200_ERR_CUDA;
+  }
   return 0;
 }
 

@@ -1,0 +1,145 @@
+// Mixture-of-experts plumbing (mixers.h): group-limited routing on fp32 scores, a counting sort of the (token, choice)
+// pairs into expert-grouped 64-row tiles for the grouped launches of linear.cu, and the weighted combine.
+//
+// Routing of one token: s = softmax(z) over all E experts; the experts form `groups` equal groups of neighbours, a group
+// is ranked by its largest s, only the `keep` best groups stay eligible; the `top` largest eligible s win, ties to the
+// lower index, and s itself (not renormalised) is the weight.  A pair's result never depends on which other pairs
+// share its tile, and the combine adds a token's choices in the order the router picked them.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+
+#include "mixers.h"
+
+namespace b200 {
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+// one warp per token; scores row in global memory is the scratch (chosen entries are overwritten with -1)
+__global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const int lane = threadIdx.x & 31;
+  float* s = scores + static_cast<long long>(t) * E;
+  float mx = -FLT_MAX;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) { const float v = expf(s[e] - mx); s[e] = v; sum += v; }
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.0f / sum;
+  for (int e = lane; e < E; e += 32) s[e] *= inv;
+  __syncwarp();
+  const int per = E / groups;
+  // keep the best groups: bit g of `kept` (lane-uniform); groups <= 64
+  unsigned long long kept = 0;
+  for (int r = 0; r < keep; ++r) {
+    float best = -1.f;
+    int bg = 0x7fffffff;
+    for (int g = lane; g < groups; g += 32) {
+      if (kept >> g & 1ull) continue;
+      float gm = -1.f;
+      for (int e = g * per; e < (g + 1) * per; ++e) gm = fmaxf(gm, s[e]);
+      if (gm > best) { best = gm; bg = g; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int og = __shfl_xor_sync(0xffffffffu, bg, o);
+      if (ob > best || (ob == best && og < bg)) { best = ob; bg = og; }
+    }
+    if (bg != 0x7fffffff) kept |= 1ull << bg;
+  }
+  for (int k = 0; k < top; ++k) {
+    float best = -1.f;
+    int be = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      if (!(kept >> (e / per) & 1ull)) continue;
+      const float v = s[e];
+      if (v > best) { best = v; be = e; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
+    }
+    if (be == 0x7fffffff) { be = 0; best = 0.f; }
+    if (lane == 0) {
+      topk_ids[static_cast<long long>(t) * top + k] = be;
+      topk_w[static_cast<long long>(t) * top + k] = best;
+      s[be] = -1.f;
+    }
+    __syncwarp();
+  }
+}
+
+// single CTA: histogram, padded offsets, scatter
+__global__ void __launch_bounds__(1024) moe_align_kernel(const int* topk_ids, int pairs, int top, int E, int* sorted_rows, int* tile_group,
+                                                         int* pair_pos, int cap) {
+  extern __shared__ int sh[];   // count[E], start[E + 1], fill[E]
+  int* count = sh;
+  int* start = sh + E;
+  int* fill = sh + 2 * E + 1;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) { count[e] = 0; fill[e] = 0; }
+  for (int i = threadIdx.x; i < cap; i += blockDim.x) sorted_rows[i] = -1;
+  for (int i = threadIdx.x; i < cap / 64; i += blockDim.x) tile_group[i] = -1;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[topk_ids[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = at;
+      const int tiles = (count[e] + 63) / 64;
+      for (int i = 0; i < tiles; ++i) tile_group[at / 64 + i] = e;
+      at += tiles * 64;
+    }
+    start[E] = at;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = topk_ids[p];
+    const int r = start[e] + atomicAdd(&fill[e], 1);
+    sorted_rows[r] = p / top;
+    pair_pos[p] = r;
+  }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const float* y, const int* pair_pos, const float* topk_w, T* out, int top, int W) {
+  const long long t = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) acc = fmaf(topk_w[t * top + k], y[static_cast<long long>(pair_pos[t * top + k]) * W + i], acc);
+    if (sizeof(T) == 2) reinterpret_cast<bf16*>(out)[t * W + i] = __float2bfloat16_rn(acc);
+    else reinterpret_cast<float*>(out)[t * W + i] = acc;
+  }
+}
+
+}  // namespace
+
+int moe_route(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (E < 1 || groups < 1 || groups > 64 || E % groups || keep < 1 || keep > groups || top < 1 || top > keep * (E / groups)) return -1;
+  moe_route_kernel<<<(T + 3) / 4, 128, 0, st>>>(scores, topk_ids, topk_w, T, E, groups, keep, top);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int moe_align(const int* topk_ids, int T, int top, int E, int* sorted_rows, int* tile_group, int* pair_pos, int cap, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (cap % 64 || cap < T * top + E * 64) return -1;
+  const size_t smem = static_cast<size_t>(3 * E + 1) * sizeof(int);
+  if (smem > 48 * 1024) return -1;
+  moe_align_kernel<<<1, 1024, smem, st>>>(topk_ids, T * top, top, E, sorted_rows, tile_group, pair_pos, cap);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int moe_combine(const float* y, const int* pair_pos, const float* topk_w, void* out, DType t, int T, int top, int W, cudaStream_t st) {
+  if (T <= 0) return 0;
+  const int th = W >= 1024 ? 256 : 128;
+  if (t == DT_BF16) moe_combine_kernel<bf16><<<T, th, 0, st>>>(y, pair_pos, topk_w, static_cast<bf16*>(out), top, W);
+  else moe_combine_kernel<float><<<T, th, 0, st>>>(y, pair_pos, topk_w, static_cast<float*>(out), top, W);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+}  // namespace b200

@@ -7,7 +7,7 @@ from dataclasses import dataclass
 
 import numpy as np
 
-from ._lib import Config, Sampling, Stats, StepInfo, Usage, check, lib
+from ._lib import Config, FeedEntry, Sampling, Stats, StepInfo, Usage, check, lib
 
 FINISH = {0: None, 1: "stop", 2: "length", 3: "aborted", 4: "error"}
 
@@ -53,12 +53,26 @@ class PollResult:
     usage: tuple
 
 
+DTYPES = {"bfloat16": 0, "bf16": 0, "float32": 1, "f32": 1}
+
+
 class Engine:
-    def __init__(self, cfg: Config):
+    def __init__(self, cfg: Config, model_dir: str | None = None, dtype: str = "bfloat16", random_weights: bool = False):
+        """cfg alone: the built-in Llama engine with seeded weights.  With model_dir: whatever design the directory's
+        config.json names (b200_engine_create_from_dir); cfg then only carries the serving limits."""
         self._l = lib()
         self._h = C.c_void_p()
         self.cfg = cfg
-        check(self._l.b200_engine_create(C.byref(cfg), C.byref(self._h)))
+        if model_dir is None:
+            check(self._l.b200_engine_create(C.byref(cfg), C.byref(self._h)))
+        else:
+            check(self._l.b200_engine_create_from_dir(str(model_dir).encode(), C.byref(cfg), DTYPES[dtype],
+                                                      1 if random_weights else 0, C.byref(self._h)))
+            import json
+            import os
+            with open(os.path.join(str(model_dir), "config.json")) as f:
+                c = json.load(f)
+            cfg.vocab = int(c.get("vocab", c.get("vocab_size", cfg.vocab)))
 
     def close(self):
         if self._h:
@@ -194,6 +208,44 @@ class Engine:
         out = np.empty((rows, self.cfg.vocab), dtype=np.uint16)
         check(self._l.b200_engine_read_logits(self._h, out.ctypes.data_as(C.c_void_p), rows))
         return (out.astype(np.uint32) << 16).view(np.float32)
+
+    # ---- fed sequences: the caller supplies every token and reads logits (b200_feed_*)
+    def feed_open(self) -> int:
+        rid = C.c_uint64()
+        check(self._l.b200_feed_open(self._h, C.byref(rid)))
+        return rid.value
+
+    def feed_close(self, rid: int):
+        check(self._l.b200_feed_close(self._h, rid))
+
+    def feed_step(self, entries) -> np.ndarray:
+        """entries: [(rid, tokens, want offsets)]; returns fp32 logits [total wanted, vocab] in entry order."""
+        arr = (FeedEntry * len(entries))()
+        keep = []
+        total = 0
+        for i, (rid, toks, want) in enumerate(entries):
+            t = np.ascontiguousarray(toks, dtype=np.int32)
+            w = np.ascontiguousarray(want, dtype=np.int32)
+            keep += [t, w]
+            arr[i].req_id = rid
+            arr[i].tokens = t.ctypes.data_as(C.POINTER(C.c_int32))
+            arr[i].n_tokens = len(t)
+            arr[i].want = w.ctypes.data_as(C.POINTER(C.c_int32)) if len(w) else None
+            arr[i].n_want = len(w)
+            total += len(w)
+        out = np.empty((total, self.cfg.vocab), dtype=np.float32)
+        check(self._l.b200_feed_step(self._h, arr, len(entries), out.ctypes.data_as(C.POINTER(C.c_float)), out.size))
+        return out
+
+    def debug_residuals(self, on: bool):
+        check(self._l.b200_engine_debug_residuals(self._h, 1 if on else 0))
+
+    def read_residuals(self) -> np.ndarray:
+        n = check(self._l.b200_engine_read_residuals(self._h, None, 0))
+        out = np.empty(n, dtype=np.float32)
+        if n:
+            check(self._l.b200_engine_read_residuals(self._h, out.ctypes.data_as(C.POINTER(C.c_float)), n))
+        return out
 
     def generate(self, prompts, max_tokens=16, max_steps=100000):
         """Manual-step helper: run all prompts to completion, return the list of token lists."""
