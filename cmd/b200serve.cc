@@ -4,7 +4,7 @@
 // in-process engine in place of backend pods.  Everything else of cmd/main.go / manager.Run (K8s manager, autoscaler,
 // messengers) is out of scope.
 //
-//   b200serve --gpus 8 --model llama-3-8b [--model-dir /models/llama-3-8b] [--strategy PrefixHash] [--port 8000]
+//   b200serve --gpus 8 --model llama-3-8b [--model-dir /models/llama-3-8b] [--dtype bfloat16|float32] [--strategy PrefixHash] [--port 8000]
 #include <signal.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -23,6 +23,7 @@ int main(int argc, char** argv) {
   int gpus = 1, port = 8000, max_seqs = 128, max_len = 2048, budget = 2048;
   std::string model = "llama-3-8b", model_dir, strategy = "LeastLoad", host = "0.0.0.0", adapters, tokenizer_path;
   double kv_fraction = 0.85;
+  int dtype = B200_DTYPE_BF16;
   unsigned long long seed = 0;
   for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];
@@ -40,11 +41,11 @@ int main(int argc, char** argv) {
     else if (a == "--max-num-batched-tokens") budget = atoi(next());
     else if (a == "--gpu-memory-utilization") kv_fraction = atof(next());
     else if (a == "--seed") seed = strtoull(next(), nullptr, 10);
+    else if (a == "--dtype") { const std::string d = next(); dtype = (d == "float32" || d == "f32") ? B200_DTYPE_F32 : B200_DTYPE_BF16; }
     else { fprintf(stderr, "unknown flag %s\n", a.c_str()); return 2; }
   }
   b200_config cfg;
   b200_config_default(&cfg);
-  if (!model_dir.empty() && b200_config_from_hf(model_dir.c_str(), &cfg)) { fprintf(stderr, "config: %s\n", b200_last_error()); return 1; }
   cfg.max_num_seqs = max_seqs;
   cfg.max_model_len = max_len;
   cfg.max_batched_tokens = budget;
@@ -54,8 +55,9 @@ int main(int argc, char** argv) {
   for (int g = 0; g < gpus; ++g) {
     cfg.device = g;
     b200_engine* e = nullptr;
-    if (b200_engine_create(&cfg, &e)) { fprintf(stderr, "engine %d: %s\n", g, b200_last_error()); return 1; }
-    if (!model_dir.empty() && b200_engine_load_safetensors(e, model_dir.c_str())) { fprintf(stderr, "load: %s\n", b200_last_error()); return 1; }
+    // a model directory's config.json picks the design (built-in Llama or a registered one) and its sizes
+    const int rc = model_dir.empty() ? b200_engine_create(&cfg, &e) : b200_engine_create_from_dir(model_dir.c_str(), &cfg, dtype, 0, &e);
+    if (rc) { fprintf(stderr, "engine %d: %s\n", g, b200_last_error()); return 1; }
     engines.push_back(e);
     fprintf(stderr, "[b200serve] replica gpu:%d ready\n", g);
   }
@@ -65,7 +67,7 @@ int main(int argc, char** argv) {
   sc.adapters = adapters.empty() ? nullptr : adapters.c_str();
   sc.strategy = strategy == "PrefixHash" ? B200_LB_PREFIX_HASH : B200_LB_LEAST_LOAD;
   sc.max_retries = 3;
-  sc.vocab = cfg.vocab;
+  sc.vocab = b200_engine_vocab(engines[0]);
   sc.max_model_len = cfg.max_model_len;
   b200_server* srv = nullptr;
   if (b200_server_create(&sc, engines.data(), gpus, &srv)) { fprintf(stderr, "server: %s\n", b200_last_error()); return 1; }

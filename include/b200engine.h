@@ -185,6 +185,8 @@ enum { B200_CREATE_RANDOM_WEIGHTS = 1 };   /* no model.safetensors in <dir>: see
  * eos_token_id, seed are taken from it, the architecture fields from the directory.  dtype: storage and arithmetic of
  * matrices and activations; B200_DTYPE_F32 runs everything in true 32-bit and exists for registered designs only. */
 int b200_engine_create_from_dir(const char* dir, const b200_config* limits, int32_t dtype, int32_t flags, b200_engine** out);
+/* Vocabulary size of the model an engine serves. */
+int32_t b200_engine_vocab(b200_engine* e);
 
 /* Fed sequences (manual_step engines): the caller supplies every token, step by step, and reads logits — replaying a
  * recorded schedule, scoring, teacher forcing.  A fed step runs exactly the listed tokens of the listed sequences as one

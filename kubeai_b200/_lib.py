@@ -144,6 +144,7 @@ SYMBOLS = {
     "b200_engine_load_safetensors": (C.c_int, [_vp, C.c_char_p]),
     "b200_safetensors_list": (C.c_int64, [C.c_char_p, C.c_char_p, C.c_size_t]),
     "b200_engine_create_from_dir": (C.c_int, [C.c_char_p, C.POINTER(Config), _i32, _i32, C.POINTER(_vp)]),
+    "b200_engine_vocab": (C.c_int32, [_vp]),
     "b200_feed_open": (C.c_int, [_vp, C.POINTER(_u64)]),
     "b200_feed_step": (C.c_int, [_vp, C.POINTER(FeedEntry), _i32, C.POINTER(C.c_float), _i64]),
     "b200_feed_close": (C.c_int, [_vp, _u64]),

@@ -2049,6 +2049,8 @@ b200::Model* b200::engine_model(b200_engine* e) { return e ? e->impl.model.get()
 
 extern "C" {
 
+int32_t b200_engine_vocab(b200_engine* e) { return e ? e->impl.V : 0; }
+
 int b200_feed_open(b200_engine* e, uint64_t* req_id) {
   if (!e || !req_id) { set_error("null argument"); return B200_ERR_INVALID; }
   Engine& g = e->impl;

@@ -68,11 +68,7 @@ class Engine:
         else:
             check(self._l.b200_engine_create_from_dir(str(model_dir).encode(), C.byref(cfg), DTYPES[dtype],
                                                       1 if random_weights else 0, C.byref(self._h)))
-            import json
-            import os
-            with open(os.path.join(str(model_dir), "config.json")) as f:
-                c = json.load(f)
-            cfg.vocab = int(c.get("vocab", c.get("vocab_size", cfg.vocab)))
+            cfg.vocab = self._l.b200_engine_vocab(self._h)
 
     def close(self):
         if self._h:

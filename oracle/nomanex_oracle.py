@@ -157,7 +157,7 @@ class NomanexOracle:
         return {k[len(pre):]: v for k, v in self.W.items() if k.startswith(pre)}
 
     def _norm(self, x, name):
-        return dyt(x, self.W[name], self.W[name + ".b"], float(self.W[name + ".alpha"]))
+        return dyt(x, self.W[name], self.W[name + ".b"], float(np.asarray(self.W[name + ".alpha"]).reshape(-1)[0]))
 
     def forward(self, tokens, return_layers=False):
         """Logits [n, vocab] of one sequence from position 0 (and the residual after every layer run)."""
@@ -165,7 +165,9 @@ class NomanexOracle:
         x = embed(tokens, self.W, cfg)
         trace = []
         for i, ly in enumerate(cfg["layers"]):
-            src = ly.get("weights_of", i)
+            src = i
+            while "weights_of" in cfg["layers"][src]:      # a layer without tensors of its own follows the reference
+                src = cfg["layers"][src]["weights_of"]
             hs = self._norm(x, "l%d.norm1" % src)
             mix = self._params(src, "mix")
             if ly["type"] == "gla":
