@@ -206,6 +206,11 @@ int b200_feed_step(b200_engine* e, const b200_feed_entry* entries, int32_t n, fl
 int b200_feed_close(b200_engine* e, uint64_t req_id);
 /* Debug (registered designs): with on != 0 every later step appends the fp32 residual stream [tokens, width] after each
  * layer run to a host buffer; read returns the number of floats held (and copies them when cap_floats suffices). */
+/* Debug (registered designs): with on != 0 every kernel of later steps is timed on the device under its name (the step then
+ * waits for each launch); kernel_times returns JSON {"name": {"us": total, "launches": n}} accumulated since it was switched
+ * on (the length needed; copied when cap suffices). */
+int b200_engine_profile_kernels(b200_engine* e, int32_t on);
+int64_t b200_engine_kernel_times(b200_engine* e, char* buf, size_t cap);
 int b200_engine_debug_residuals(b200_engine* e, int32_t on);
 int64_t b200_engine_read_residuals(b200_engine* e, float* out, int64_t cap_floats);
 

@@ -148,6 +148,8 @@ SYMBOLS = {
     "b200_feed_open": (C.c_int, [_vp, C.POINTER(_u64)]),
     "b200_feed_step": (C.c_int, [_vp, C.POINTER(FeedEntry), _i32, C.POINTER(C.c_float), _i64]),
     "b200_feed_close": (C.c_int, [_vp, _u64]),
+    "b200_engine_profile_kernels": (C.c_int, [_vp, _i32]),
+    "b200_engine_kernel_times": (C.c_int64, [_vp, C.c_char_p, C.c_size_t]),
     "b200_engine_debug_residuals": (C.c_int, [_vp, _i32]),
     "b200_engine_read_residuals": (C.c_int64, [_vp, C.POINTER(C.c_float), _i64]),
     "b200_router_create": (C.c_int, [_i32, C.POINTER(_vp)]),

@@ -1503,7 +1503,14 @@ int Engine::feed_step(const b200_feed_entry* entries, int n, float* logits_out, 
   StepMeta m;
   int rc = pack(&f, &want, &m);
   if (!rc) {
-    int32_t* dbuf = stage_dev[ring_n - 1];
+    int slot = ring_n - 1;   // scratch, unless steps are being recorded for replay / per-class profiling
+    if (recording && ring_n > 1) {
+      slot = ring_pos;
+      ring_pos = (ring_pos + 1) % (ring_n - 1);
+      ++recorded;
+    }
+    ring_meta[slot] = m;
+    int32_t* dbuf = stage_dev[slot];
     CK(cudaMemcpyAsync(dbuf, stage_host, static_cast<size_t>(m.words) * 4, cudaMemcpyHostToDevice, stream));
     CK(cudaEventRecord(ev0, stream));
     if (model) rc = forward_model(m, dbuf, logits_out);
@@ -2087,6 +2094,27 @@ int b200_feed_close(b200_engine* e, uint64_t req_id) {
   std::lock_guard<std::mutex> lk(g.mu_);
   g.stats.kv_blocks_free = g.pool.free_count();
   return 0;
+}
+
+int b200_engine_profile_kernels(b200_engine* e, int32_t on) {
+  if (!e || !e->impl.model) { set_error("kernel profiling by name needs an engine around a registered design"); return B200_ERR_INVALID; }
+  e->impl.model->profile_kernels = on != 0;
+  e->impl.model->kernel_times.clear();
+  return 0;
+}
+
+int64_t b200_engine_kernel_times(b200_engine* e, char* buf, size_t cap) {
+  if (!e || !e->impl.model) { set_error("kernel profiling by name needs an engine around a registered design"); return B200_ERR_INVALID; }
+  std::string o = "{";
+  for (auto& kv : e->impl.model->kernel_times) {
+    char tmp[160];
+    snprintf(tmp, sizeof(tmp), "%s\"%s\":{\"us\":%.3f,\"launches\":%lld}", o.size() > 1 ? "," : "", kv.first.c_str(), kv.second.first,
+             static_cast<long long>(kv.second.second));
+    o += tmp;
+  }
+  o += "}";
+  if (buf && cap > o.size()) memcpy(buf, o.c_str(), o.size() + 1);
+  return static_cast<int64_t>(o.size());
 }
 
 int b200_engine_debug_residuals(b200_engine* e, int32_t on) {

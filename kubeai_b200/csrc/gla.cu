@@ -22,13 +22,17 @@ __device__ __forceinline__ void stf(float* p, float v) { *p = v; }
 __device__ __forceinline__ void stf(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
 constexpr int kRows = 32;      // key rows of the state held by one thread
-constexpr int kGroup = 8;      // tokens staged per shared-memory round
+constexpr int kGroup = 16;     // tokens staged per shared-memory round (fewer when dim is large)
 constexpr int kThreads = 128;
 
-// grid: (ceil(vdim / (kThreads / P)), heads, nseq); P = row slices per column (a power of two, P * kRows >= dim)
+// grid: (ceil(vdim / (kThreads / P)), heads, nseq); P = row slices per column (a power of two), rpp = key rows per slice
+// (a multiple of 4, P * rpp >= dim, rpp <= kRows).  G tokens are staged per round: q (scaled), k, alpha as [G][3][P][rpp + 4]
+// (rows past dim are zeros; the 4-float pad puts the P slices a thread group reads at once into different banks, and a
+// thread reads its slice as float4), then v and o for the CTA's columns [G][cols] each, so the sequential token loop
+// touches shared memory only.
 template <typename T>
-__global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, int rows_per_part) {
-  extern __shared__ float sm[];   // [kGroup][3][dim]: q (scaled), k, alpha
+__global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, int rpp, int G) {
+  extern __shared__ __align__(16) float sm[];
   const int seq = blockIdx.z, head = blockIdx.y;
   const int tok0 = a.seqs[seq * 8 + 0], n = a.seqs[seq * 8 + 1], pos0 = a.seqs[seq * 8 + 2], slot = a.seqs[seq * 8 + 3];
   const int D = a.dim, Dv = a.vdim;
@@ -36,55 +40,77 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
   const int cols = kThreads / P;
   const int j = blockIdx.x * cols + jj;
   const bool live = j < Dv;
-  const int i0 = part * rows_per_part;
+  const int i0 = part * rpp;
+  const int ps = rpp + 4, Dp = P * ps;     // padded slice and row length
+  float* vs = sm + static_cast<size_t>(G) * 3 * Dp;
+  float* os = vs + G * cols;
   const T* base = static_cast<const T*>(a.qkv);
   float* Sg = a.states + ((static_cast<long long>(slot) * a.heads + head) * D) * Dv;
   float S[kRows];
 #pragma unroll
   for (int r = 0; r < kRows; ++r) {
     const int i = i0 + r;
-    S[r] = (live && r < rows_per_part && i < D && pos0 > 0) ? Sg[static_cast<long long>(i) * Dv + j] : 0.f;
+    S[r] = (live && r < rpp && i < D && pos0 > 0) ? Sg[static_cast<long long>(i) * Dv + j] : 0.f;
   }
-  for (int g0 = 0; g0 < n; g0 += kGroup) {
-    const int gn = min(kGroup, n - g0);
+  const int slice_elems = P * rpp;
+  for (int g0 = 0; g0 < n; g0 += G) {
+    const int gn = min(G, n - g0);
     __syncthreads();
-    for (int e = threadIdx.x; e < gn * D; e += kThreads) {
-      const int tt = e / D, i = e - tt * D;
-      const long long row = static_cast<long long>(tok0 + g0 + tt);
-      const T* rp = base + row * a.ld;
-      const int c = head * D + i;
-      const float z = a.z[row * (a.heads * D) + c] + a.z_bias[c];
-      // log sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
-      const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
-      float* s3 = sm + (tt * 3) * D;
-      s3[i] = ldf(rp + a.q_off + c) * a.q_scale;
-      s3[D + i] = ldf(rp + a.k_off + c);
-      s3[2 * D + i] = expf(ls * a.inv_tau);
+    for (int e = threadIdx.x; e < gn * slice_elems; e += kThreads) {
+      const int tt = e / slice_elems, x = e - tt * slice_elems, pp = x / rpp, r = x - pp * rpp, i = pp * rpp + r;
+      float qv = 0.f, kv = 0.f, av = 0.f;
+      if (i < D) {
+        const long long row = static_cast<long long>(tok0 + g0 + tt);
+        const T* rp = base + row * a.ld;
+        const int c = head * D + i;
+        const float z = a.z[row * (a.heads * D) + c] + a.z_bias[c];
+        // log sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
+        const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+        qv = ldf(rp + a.q_off + c) * a.q_scale;
+        kv = ldf(rp + a.k_off + c);
+        av = expf(ls * a.inv_tau);
+      }
+      float* s3 = sm + (tt * 3) * Dp + pp * ps + r;
+      s3[0] = qv;
+      s3[Dp] = kv;
+      s3[2 * Dp] = av;
+    }
+    for (int e = threadIdx.x; e < gn * cols; e += kThreads) {
+      const int tt = e / cols, c = e - tt * cols, jc = blockIdx.x * cols + c;
+      vs[e] = jc < Dv ? ldf(base + static_cast<long long>(tok0 + g0 + tt) * a.ld + a.v_off + head * Dv + jc) : 0.f;
     }
     __syncthreads();
     for (int tt = 0; tt < gn; ++tt) {
-      const long long row = static_cast<long long>(tok0 + g0 + tt);
-      const float v = live ? ldf(base + row * a.ld + a.v_off + head * Dv + j) : 0.f;
-      const float* q = sm + (tt * 3) * D + i0;
-      const float* k = q + D;
-      const float* al = k + D;
-      float o = 0.f;
+      const float v = vs[tt * cols + jj];
+      const float4* q4 = reinterpret_cast<const float4*>(sm + (tt * 3) * Dp + part * ps);
+      const float4* k4 = reinterpret_cast<const float4*>(sm + (tt * 3 + 1) * Dp + part * ps);
+      const float4* a4 = reinterpret_cast<const float4*>(sm + (tt * 3 + 2) * Dp + part * ps);
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-      for (int r = 0; r < kRows; ++r) {
-        if (r < rows_per_part && i0 + r < D) {
-          S[r] = fmaf(al[r], S[r], k[r] * v);
-          o = fmaf(S[r], q[r], o);
+      for (int m = 0; m < kRows / 4; ++m) {
+        if (4 * m < rpp) {
+          const float4 qa = q4[m], ka = k4[m], aa = a4[m];
+          S[4 * m] = fmaf(aa.x, S[4 * m], ka.x * v);         o0 = fmaf(S[4 * m], qa.x, o0);
+          S[4 * m + 1] = fmaf(aa.y, S[4 * m + 1], ka.y * v); o1 = fmaf(S[4 * m + 1], qa.y, o1);
+          S[4 * m + 2] = fmaf(aa.z, S[4 * m + 2], ka.z * v); o2 = fmaf(S[4 * m + 2], qa.z, o2);
+          S[4 * m + 3] = fmaf(aa.w, S[4 * m + 3], ka.w * v); o3 = fmaf(S[4 * m + 3], qa.w, o3);
         }
       }
+      float o = (o0 + o1) + (o2 + o3);
       for (int w = 1; w < P; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
-      if (live && part == 0) a.o[row * (a.heads * Dv) + head * Dv + j] = o;
+      if (part == 0) os[tt * cols + jj] = o;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < gn * cols; e += kThreads) {
+      const int tt = e / cols, c = e - tt * cols, jc = blockIdx.x * cols + c;
+      if (jc < Dv) a.o[static_cast<long long>(tok0 + g0 + tt) * (a.heads * Dv) + head * Dv + jc] = os[e];
     }
   }
   if (live) {
 #pragma unroll
     for (int r = 0; r < kRows; ++r) {
       const int i = i0 + r;
-      if (r < rows_per_part && i < D) Sg[static_cast<long long>(i) * Dv + j] = S[r];
+      if (r < rpp && i < D) Sg[static_cast<long long>(i) * Dv + j] = S[r];
     }
   }
 }
@@ -116,13 +142,16 @@ int gla_scan(const GlaArgs& a, cudaStream_t st) {
   int P = 1;
   while (P * kRows < a.dim) P <<= 1;
   if (P > 32) return -1;   // dim <= 1024
-  const int rows_per_part = (a.dim + P - 1) / P;
+  const int rows_per_part = ((a.dim + P - 1) / P + 3) / 4 * 4;
   const int cols = kThreads / P;
   dim3 grid((a.vdim + cols - 1) / cols, a.heads, a.nseq);
-  const size_t smem = static_cast<size_t>(kGroup) * 3 * a.dim * sizeof(float);
+  int G = kGroup;
+  auto smem_for = [&](int g) { return static_cast<size_t>(g) * (3 * P * (rows_per_part + 4) + 2 * cols) * sizeof(float); };
+  while (G > 1 && smem_for(G) > 44 * 1024) G >>= 1;
+  const size_t smem = smem_for(G);
   if (smem > 48 * 1024) return -1;
-  if (a.t == DT_BF16) gla_scan_kernel<bf16><<<grid, kThreads, smem, st>>>(a, P, rows_per_part);
-  else gla_scan_kernel<float><<<grid, kThreads, smem, st>>>(a, P, rows_per_part);
+  if (a.t == DT_BF16) gla_scan_kernel<bf16><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G);
+  else gla_scan_kernel<float><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

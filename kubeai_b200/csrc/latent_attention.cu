@@ -12,8 +12,12 @@
 #include <float.h>
 #include <math.h>
 
+#include <stdlib.h>
+
+#include <atomic>
 #include <vector>
 
+#include "launch.h"
 #include "mixers.h"
 
 namespace b200 {
@@ -139,6 +143,207 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(LatentAttnArgs a) {
   }
 }
 
+// ---------------------------------------------------------------- tensor-core kernel (bf16 cache)
+// One CTA = 16 query rows = TQ consecutive tokens of one sequence x HB heads (HB = min(heads, 16), TQ = 16 / HB), 8 warps.
+// The window of the tile's tokens is walked in tiles of 64 keys, gathered from the pages into shared memory by cp.async
+// (double buffered).  Per key tile: warp w multiplies the 16 latent queries with its 8 keys over the whole latent width
+// (mma.sync m16n8k16, fragments by ldmatrix), the scores go through shared memory to a 256-thread online-softmax pass
+// (fp32 running maximum and sum per row, window and causal mask per row), and every warp then accumulates its own
+// columns of sum_j p_j c_j from the same key tile (ldmatrix.trans), rescaled when a row's maximum moves.
+constexpr int kKeys = 64;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+constexpr int kMaxPairs = 4;   // 16-column pairs of the latent value width per warp: kv_rank <= 8 * 4 * 16 = 512
+
+__global__ void __launch_bounds__(256) latent_attn_mma_kernel(LatentAttnArgs a, const int* seqs, int nseq, int TQ, int HB) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int C = a.kv_rank, E = a.kv_rank + a.rot_dim, LDE = E + 8;
+  bf16* Qs = reinterpret_cast<bf16*>(smraw);                       // [16][LDE]
+  bf16* Ks = Qs + 16 * LDE;                                        // [2][kKeys][LDE]
+  float* Ss = reinterpret_cast<float*>(Ks + 2 * kKeys * LDE);      // [16][kKeys + 4]
+  bf16* Ps = reinterpret_cast<bf16*>(Ss + 16 * (kKeys + 4));       // [16][kKeys + 8]
+  float* Ms = reinterpret_cast<float*>(Ps + 16 * (kKeys + 8));     // running max [16], sum [16], rescale [16]
+  float* Ls = Ms + 16;
+  float* As = Ls + 16;
+  // which (sequence, token tile) is this CTA's
+  int idx = blockIdx.x, seq = -1, tile = 0;
+  for (int s = 0; s < nseq; ++s) {
+    const int tiles = (seqs[s * 8 + 1] + TQ - 1) / TQ;
+    if (idx < tiles) { seq = s; tile = idx; break; }
+    idx -= tiles;
+  }
+  if (seq < 0) return;
+  const int tok0 = seqs[seq * 8 + 0], n = seqs[seq * 8 + 1], pos0 = seqs[seq * 8 + 2];
+  const int tq0 = tile * TQ, ntq = min(TQ, n - tq0);
+  const int h0 = blockIdx.y * HB;
+  const int p_first = pos0 + tq0, p_last = p_first + ntq - 1;
+  const int lo = max(0, p_first - a.window + 1);
+  const int ntiles = (p_last - lo) / kKeys + 1;
+  const int* bt = a.block_tables + static_cast<long long>(seq) * a.max_blocks;
+  const bf16* cache = static_cast<const bf16*>(a.cache);
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int chunks = E / 8;   // 16-byte pieces of one cache row
+
+  auto load_tile = [&](int ti, int buf) {
+    bf16* dst = Ks + static_cast<size_t>(buf) * kKeys * LDE;
+    const int j0 = lo + ti * kKeys;
+    for (int e = tid; e < kKeys * chunks; e += 256) {
+      const int jt = e / chunks, c = e - jt * chunks, j = j0 + jt;
+      bf16* d = dst + jt * LDE + c * 8;
+      if (j <= p_last) cp_async16(smem_addr(d), cache + (static_cast<long long>(bt[j / a.page]) * a.page + j % a.page) * E + c * 8);
+      else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+    }
+  };
+  load_tile(0, 0);
+  // latent queries of the 16 rows (row r = token tq0 + r / HB, head h0 + r % HB), rounded to bf16
+  for (int e = tid; e < 16 * E; e += 256) {
+    const int r = e / E, c = e - r * E, tq = r / HB, h = h0 + r % HB;
+    float v = 0.f;
+    if (tq < ntq && h < a.heads) v = a.qlat[(static_cast<long long>(tok0 + tq0 + tq) * a.heads + h) * E + c];
+    Qs[r * LDE + c] = __float2bfloat16_rn(v);
+  }
+  if (tid < 16) { Ms[tid] = -FLT_MAX; Ls[tid] = 0.f; As[tid] = 1.f; }
+  float acc[kMaxPairs][2][4];
+#pragma unroll
+  for (int i = 0; i < kMaxPairs; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[i][j][k] = 0.f;
+  const int npairs = C / 16;
+  const int g = lane >> 2, t4 = lane & 3;
+  // softmax pass: thread -> (row, 4 keys)
+  const int srow = tid >> 4, sk = (tid & 15) * 4;
+  const int s_tq = srow / HB;
+  const bool s_valid = s_tq < ntq && h0 + srow % HB < a.heads;
+  const int s_pos = p_first + s_tq;
+
+  for (int ti = 0; ti < ntiles; ++ti) {
+    cp_async_wait_all();
+    __syncthreads();
+    if (ti + 1 < ntiles) load_tile(ti + 1, (ti + 1) & 1);
+    const bf16* Kt = Ks + static_cast<size_t>(ti & 1) * kKeys * LDE;
+    // ---- scores of this warp's 8 keys
+    {
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint32_t qa = smem_addr(Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDE + 8 * (lane >> 4));
+      const uint32_t ka = smem_addr(Kt + (8 * w + (lane & 7)) * LDE + 8 * (lane >> 3));
+      for (int ks = 0; ks < E; ks += 32) {
+        uint32_t bq[4], a0[4];
+        ldsm_x4(bq, ka + ks * 2);   // keys x k [ks, ks + 32): b0, b1 of two k-steps
+        ldsm_x4(a0, qa + ks * 2);
+        mma16816(c, a0, bq[0], bq[1]);
+        if (ks + 16 < E) {
+          uint32_t a1[4];
+          ldsm_x4(a1, qa + (ks + 16) * 2);
+          mma16816(c, a1, bq[2], bq[3]);
+        }
+      }
+      float* sp = Ss + g * (kKeys + 4) + 8 * w + 2 * t4;
+      sp[0] = c[0]; sp[1] = c[1];
+      sp[8 * (kKeys + 4)] = c[2]; sp[8 * (kKeys + 4) + 1] = c[3];
+    }
+    __syncthreads();
+    // ---- online softmax
+    {
+      const int j0 = lo + ti * kKeys + sk;
+      float sv[4], mx = -FLT_MAX;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int j = j0 + i;
+        const bool vis = s_valid && j <= s_pos && j > s_pos - a.window;
+        sv[i] = vis ? Ss[srow * (kKeys + 4) + sk + i] * a.scale : -FLT_MAX;
+        mx = fmaxf(mx, sv[i]);
+      }
+      const float m_old = Ms[srow];
+      for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float m_new = fmaxf(m_old, mx);
+      float sum = 0.f;
+      __nv_bfloat162 p01, p23;
+      float pv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { pv[i] = sv[i] == -FLT_MAX ? 0.f : expf(sv[i] - m_new); sum += pv[i]; }
+      for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      p01 = __floats2bfloat162_rn(pv[0], pv[1]);
+      p23 = __floats2bfloat162_rn(pv[2], pv[3]);
+      *reinterpret_cast<__nv_bfloat162*>(Ps + srow * (kKeys + 8) + sk) = p01;
+      *reinterpret_cast<__nv_bfloat162*>(Ps + srow * (kKeys + 8) + sk + 2) = p23;
+      if ((tid & 15) == 0) {
+        const float al = m_old == -FLT_MAX ? 0.f : expf(m_old - m_new);
+        Ms[srow] = m_new;
+        Ls[srow] = Ls[srow] * al + sum;
+        As[srow] = m_new == -FLT_MAX ? 1.f : al;
+      }
+    }
+    __syncthreads();
+    // ---- values: this warp's column pairs
+    {
+      const float al0 = As[g], al1 = As[g + 8];
+      uint32_t pa[4][4];
+      const uint32_t pbase = smem_addr(Ps + ((lane & 7) + 8 * ((lane >> 3) & 1)) * (kKeys + 8) + 8 * (lane >> 4));
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) ldsm_x4(pa[ks], pbase + ks * 32);
+#pragma unroll
+      for (int i = 0; i < kMaxPairs; ++i) {
+        const int pp = w + 8 * i;
+        if (pp < npairs) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j) { acc[i][j][0] *= al0; acc[i][j][1] *= al0; acc[i][j][2] *= al1; acc[i][j][3] *= al1; }
+          const uint32_t vb = smem_addr(Kt + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDE + 16 * pp + 8 * (lane >> 4));
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            uint32_t bv[4];
+            ldsm_x4_trans(bv, vb + ks * 16 * LDE * 2);
+            mma16816(acc[i][0], pa[ks], bv[0], bv[1]);
+            mma16816(acc[i][1], pa[ks], bv[2], bv[3]);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // ---- normalise and store: rows g and g + 8
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = g + 8 * half, tq = r / HB, h = h0 + r % HB;
+    if (tq >= ntq || h >= a.heads) continue;
+    const float inv = 1.0f / Ls[r];
+    float* out = a.olat + (static_cast<long long>(tok0 + tq0 + tq) * a.heads + h) * C;
+#pragma unroll
+    for (int i = 0; i < kMaxPairs; ++i) {
+      const int pp = w + 8 * i;
+      if (pp < npairs) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          out[16 * pp + 8 * j + 2 * t4] = acc[i][j][2 * half] * inv;
+          out[16 * pp + 8 * j + 2 * t4 + 1] = acc[i][j][2 * half + 1] * inv;
+        }
+      }
+    }
+  }
+}
+
+size_t latent_mma_smem(int E) {
+  const size_t LDE = E + 8;
+  return (16 * LDE + 2 * kKeys * LDE) * 2 + 16 * (kKeys + 4) * 4 + 16 * (kKeys + 8) * 2 + 3 * 16 * 4;
+}
+
 }  // namespace
 
 int rope_table_interleaved(float2* table, int max_pos, int dims, double base, cudaStream_t st) {
@@ -167,6 +372,20 @@ int latent_prep(const LatentPrepArgs& a, cudaStream_t st) {
 int latent_attention(const LatentAttnArgs& a, cudaStream_t st) {
   if (a.T <= 0) return 0;
   if (a.window < 1) return -1;
+  // bf16 caches whose widths fit the fragments run on the tensor cores (B200_NX_ATTN_MMA=0: A/B knob)
+  const int E = a.kv_rank + a.rot_dim;
+  const char* ev = getenv("B200_NX_ATTN_MMA");
+  if (a.t == DT_BF16 && a.seqs && E % 16 == 0 && a.kv_rank % 16 == 0 && a.kv_rank <= 8 * kMaxPairs * 16 && latent_mma_smem(E) <= 220 * 1024 &&
+      !(ev && atoi(ev) == 0)) {
+    const int HB = a.heads < 16 ? a.heads : 16, TQ = 16 / HB;
+    const size_t smem = latent_mma_smem(E);
+    static std::atomic<unsigned long long> attr_done{0};
+    // once per device, for the largest tile the dispatch admits: the attribute is a limit, not a per-launch size
+    if (!ensure_dynamic_smem(latent_attn_mma_kernel, 220 * 1024, &attr_done)) return -2;
+    dim3 grid((a.T + TQ - 1) / TQ + a.nseq, (a.heads + HB - 1) / HB);
+    latent_attn_mma_kernel<<<grid, 256, smem, st>>>(a, a.seqs, a.nseq, TQ, HB);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   const size_t smem = static_cast<size_t>(a.kv_rank + a.rot_dim + a.window) * sizeof(float);
   if (smem > 200 * 1024) return -1;
   dim3 grid(a.T, a.heads);

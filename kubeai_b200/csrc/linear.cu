@@ -4,8 +4,8 @@
 // projection path of every shape the tcgen05 GEMMs (gemm2_tcgen05.cu: bf16, K % 8 == 0, bf16 output) do not take:
 // fp32 models, fp32 outputs (router logits, decay pre-activations, latent queries), odd sizes, gathers.
 //
-// Two kernels: a 64 x 64 x 32 shared-memory tile kernel (k ascending, so one output element is accumulated in the same
-// order whatever else is in the batch), and a one-warp-per-output-row kernel for steps of at most 8 rows (decode), which
+// Kernels: a 64 x 64 x 32 shared-memory tile kernel (fp32 weights: FMA, k ascending; bf16 weights: mma.sync tensor-core
+// products; either way one output element is accumulated in an order that does not depend on what else is in the batch), and a one-warp-per-output-row kernel for steps of at most 8 rows (decode), which
 // streams each weight row once with 16-byte loads.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -108,6 +108,92 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(LinearArgs a) {
   }
 }
 
+// bf16 weights: the same 64 x 64 x 32 tile with the products on the tensor cores (mma.sync m16n8k16, fp32 accumulators).
+// X is staged as bf16 (an fp32 X is rounded here); 8 warps = 4 row blocks x 2 column halves, a warp owns 16 rows x 32 columns.
+__device__ __forceinline__ void mma_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ bf16 to_bf16(float v) { return __float2bfloat16_rn(v); }
+__device__ __forceinline__ bf16 to_bf16(bf16 v) { return v; }
+
+template <typename TX, typename TY>
+__global__ void __launch_bounds__(256) linear_tile_mma_kernel(LinearArgs a) {
+  constexpr int LD = BK + 8;   // 80-byte rows: the 8 rows of a fragment fall into distinct banks
+  __shared__ __align__(16) bf16 Xs[BM][LD];
+  __shared__ __align__(16) bf16 Ws[BN][LD];
+  const int tid = threadIdx.x, lane = tid & 31, wrp = tid >> 5;
+  const int row0 = blockIdx.y * BM, col0 = blockIdx.x * BN;
+  const long long b = blockIdx.z;
+  const TX* X = static_cast<const TX*>(a.X) + b * a.xbs;
+  const bf16* W = static_cast<const bf16*>(a.W) + b * a.wbs;
+  TY* Y = static_cast<TY*>(a.Y) + b * a.ybs;
+  if (a.tile_group) {
+    const int g = a.tile_group[blockIdx.y];
+    if (g < 0) return;
+    W += static_cast<long long>(g) * a.wbs;
+  }
+  long long xoff[8], woff[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = wrp + 8 * i;
+    int t = row0 + r;
+    if (t >= a.T) t = -1;
+    else if (a.x_rows) t = a.x_rows[t];
+    xoff[i] = t < 0 ? -1 : static_cast<long long>(t) * a.ldx;
+    const int n = col0 + r;
+    woff[i] = n < a.N ? static_cast<long long>(n) * a.ldw : -1;
+  }
+  const int wm = wrp & 3, wn = wrp >> 2, g = lane >> 2, t4 = lane & 3;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  const bf16 zero = __float2bfloat16_rn(0.f);
+  for (int k0 = 0; k0 < a.K; k0 += BK) {
+    const int k = k0 + lane;
+    const bool kin = k < a.K;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = wrp + 8 * i;
+      Xs[r][lane] = (kin && xoff[i] >= 0) ? to_bf16(X[xoff[i] + k]) : zero;
+      Ws[r][lane] = (kin && woff[i] >= 0) ? W[woff[i] + k] : zero;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < BK; ks += 16) {
+      uint32_t af[4];
+      af[0] = *reinterpret_cast<const uint32_t*>(&Xs[16 * wm + g][ks + 2 * t4]);
+      af[1] = *reinterpret_cast<const uint32_t*>(&Xs[16 * wm + g + 8][ks + 2 * t4]);
+      af[2] = *reinterpret_cast<const uint32_t*>(&Xs[16 * wm + g][ks + 2 * t4 + 8]);
+      af[3] = *reinterpret_cast<const uint32_t*>(&Xs[16 * wm + g + 8][ks + 2 * t4 + 8]);
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb) {
+        const int n = 32 * wn + 8 * nb + g;
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&Ws[n][ks + 2 * t4]);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&Ws[n][ks + 2 * t4 + 8]);
+        mma_16816(acc[nb], af, b0, b1);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int t = row0 + 16 * wm + g + 8 * half;
+    if (t >= a.T) continue;
+    if (a.x_rows && a.x_rows[t] < 0) continue;
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int n = col0 + 32 * wn + 8 * nb + 2 * t4 + j;
+        if (n < a.N) st1(Y + static_cast<long long>(t) * a.ldy + n, apply_act(acc[nb][2 * half + j], a.act));
+      }
+  }
+}
+
 // T <= 8 rows: one warp per output column n streams W[n, :] once and keeps the T accumulators in registers.
 template <typename TX, typename TW, typename TY, int VEC>
 __global__ void __launch_bounds__(256) linear_rows_kernel(LinearArgs a) {
@@ -158,7 +244,8 @@ int launch_linear(const LinearArgs& a, cudaStream_t st) {
     else linear_rows_kernel<TX, TW, TY, 1><<<grid, 256, 0, st>>>(a);
   } else {
     dim3 grid((a.N + BN - 1) / BN, (a.T + BM - 1) / BM, a.batch);
-    linear_tile_kernel<TX, TW, TY><<<grid, 256, 0, st>>>(a);
+    if constexpr (sizeof(TW) == 2) linear_tile_mma_kernel<TX, TY><<<grid, 256, 0, st>>>(a);
+    else linear_tile_kernel<TX, TW, TY><<<grid, 256, 0, st>>>(a);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -101,6 +101,7 @@ struct LatentAttnArgs {
   const int* positions; const int* seq_of_tok; const int* block_tables; int max_blocks, page;
   float* olat;
   int T, heads, kv_rank, rot_dim, window; float scale;
+  const int* seqs; int nseq;   // the step's per-sequence table ({first row, rows, first position, ...}); needed by the tensor-core kernel
 };
 int latent_attention(const LatentAttnArgs& a, cudaStream_t st);
 
@@ -111,8 +112,13 @@ int latent_attention(const LatentAttnArgs& a, cudaStream_t st);
 int moe_route(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, cudaStream_t st);
 // Sort the T * top (token, choice) pairs by expert into 64-row tiles: sorted_rows[cap] = token of each sorted row or -1,
 // tile_group[cap / 64] = expert of each tile or -1, pair_pos[T * top] = sorted row of each pair.  cap >= T*top + E*64.
-int moe_align(const int* topk_ids, int T, int top, int E, int* sorted_rows, int* tile_group, int* pair_pos, int cap, cudaStream_t st);
-// out[t] = sum_k topk_w[t, k] * y[pair_pos[t * top + k]]   (y fp32 [cap, W], k ascending)
-int moe_combine(const float* y, const int* pair_pos, const float* topk_w, void* out, DType t, int T, int top, int W, cudaStream_t st);
+// expert_rows (optional): [E][2] = {first sorted row, rows} of every expert.
+int moe_align(const int* topk_ids, int T, int top, int E, int* sorted_rows, int* tile_group, int* pair_pos, int cap, cudaStream_t st,
+              int* expert_rows = nullptr);
+// out[t] = sum_k topk_w[t, k] * y[pair_pos[t * top + k]]   (y [cap, W] fp32 or bf16, k ascending)
+int moe_combine(const void* y, DType ty, const int* pair_pos, const float* topk_w, void* out, DType t, int T, int top, int W, cudaStream_t st);
+// bf16 helpers of the per-expert tensor-core path: x rows in sorted order (negative source row -> zeros), max(p, 0)^2 in place
+int moe_gather_bf16(const void* x, const int* sorted_rows, void* out, int rows, int W, cudaStream_t st);
+int relu2_bf16(void* p, long long n, cudaStream_t st);
 
 }  // namespace b200

@@ -68,6 +68,9 @@ class Model {
   virtual int forward(const StepBatch& b, int* sampled, float* host_logits, int64_t* launches) = 0;
   // debug: when set, forward() appends the fp32 residual [T, width] after every layer run (synchronising)
   std::vector<float>* residual_sink = nullptr;
+  // debug: per-kernel device time; when on, forward() waits for every launch (name -> (microseconds, launches))
+  bool profile_kernels = false;
+  std::unordered_map<std::string, std::pair<double, int64_t>> kernel_times;
   std::unordered_map<std::string, TensorRef> tensors;   // named device tensors (weights), for inspection
 };
 

@@ -75,7 +75,7 @@ __global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, in
 
 // single CTA: histogram, padded offsets, scatter
 __global__ void __launch_bounds__(1024) moe_align_kernel(const int* topk_ids, int pairs, int top, int E, int* sorted_rows, int* tile_group,
-                                                         int* pair_pos, int cap) {
+                                                         int* pair_pos, int cap, int* expert_rows) {
   extern __shared__ int sh[];   // count[E], start[E + 1], fill[E]
   int* count = sh;
   int* start = sh + E;
@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* topk_ids, in
     int at = 0;
     for (int e = 0; e < E; ++e) {
       start[e] = at;
+      if (expert_rows) { expert_rows[2 * e] = at; expert_rows[2 * e + 1] = count[e]; }
       const int tiles = (count[e] + 63) / 64;
       for (int i = 0; i < tiles; ++i) tile_group[at / 64 + i] = e;
       at += tiles * 64;
@@ -105,12 +106,15 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* topk_ids, in
   }
 }
 
-template <typename T>
-__global__ void moe_combine_kernel(const float* y, const int* pair_pos, const float* topk_w, T* out, int top, int W) {
+__device__ __forceinline__ float ldy(const float* p) { return *p; }
+__device__ __forceinline__ float ldy(const bf16* p) { return __bfloat162float(*p); }
+
+template <typename T, typename TYIN>
+__global__ void moe_combine_kernel(const TYIN* y, const int* pair_pos, const float* topk_w, T* out, int top, int W) {
   const long long t = blockIdx.x;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     float acc = 0.f;
-    for (int k = 0; k < top; ++k) acc = fmaf(topk_w[t * top + k], y[static_cast<long long>(pair_pos[t * top + k]) * W + i], acc);
+    for (int k = 0; k < top; ++k) acc = fmaf(topk_w[t * top + k], ldy(y + static_cast<long long>(pair_pos[t * top + k]) * W + i), acc);
     if (sizeof(T) == 2) reinterpret_cast<bf16*>(out)[t * W + i] = __float2bfloat16_rn(acc);
     else reinterpret_cast<float*>(out)[t * W + i] = acc;
   }
@@ -125,20 +129,58 @@ int moe_route(float* scores, int* topk_ids, float* topk_w, int T, int E, int gro
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-int moe_align(const int* topk_ids, int T, int top, int E, int* sorted_rows, int* tile_group, int* pair_pos, int cap, cudaStream_t st) {
+int moe_align(const int* topk_ids, int T, int top, int E, int* sorted_rows, int* tile_group, int* pair_pos, int cap, cudaStream_t st,
+              int* expert_rows) {
   if (T <= 0) return 0;
   if (cap % 64 || cap < T * top + E * 64) return -1;
   const size_t smem = static_cast<size_t>(3 * E + 1) * sizeof(int);
   if (smem > 48 * 1024) return -1;
-  moe_align_kernel<<<1, 1024, smem, st>>>(topk_ids, T * top, top, E, sorted_rows, tile_group, pair_pos, cap);
+  moe_align_kernel<<<1, 1024, smem, st>>>(topk_ids, T * top, top, E, sorted_rows, tile_group, pair_pos, cap, expert_rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-int moe_combine(const float* y, const int* pair_pos, const float* topk_w, void* out, DType t, int T, int top, int W, cudaStream_t st) {
+int moe_combine(const void* y, DType ty, const int* pair_pos, const float* topk_w, void* out, DType t, int T, int top, int W, cudaStream_t st) {
   if (T <= 0) return 0;
   const int th = W >= 1024 ? 256 : 128;
-  if (t == DT_BF16) moe_combine_kernel<bf16><<<T, th, 0, st>>>(y, pair_pos, topk_w, static_cast<bf16*>(out), top, W);
-  else moe_combine_kernel<float><<<T, th, 0, st>>>(y, pair_pos, topk_w, static_cast<float*>(out), top, W);
+  if (ty == DT_BF16) {
+    if (t != DT_BF16) return -1;
+    moe_combine_kernel<bf16, bf16><<<T, th, 0, st>>>(static_cast<const bf16*>(y), pair_pos, topk_w, static_cast<bf16*>(out), top, W);
+  } else if (t == DT_BF16) moe_combine_kernel<bf16, float><<<T, th, 0, st>>>(static_cast<const float*>(y), pair_pos, topk_w, static_cast<bf16*>(out), top, W);
+  else moe_combine_kernel<float, float><<<T, th, 0, st>>>(static_cast<const float*>(y), pair_pos, topk_w, static_cast<float*>(out), top, W);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+namespace {
+// rows of x in expert-sorted order (16-byte pieces; W % 8 == 0): a negative source row becomes zeros
+__global__ void moe_gather_kernel(const uint4* x, const int* sorted_rows, uint4* out, int pieces, long long total) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long r = i / pieces;
+  const int c = static_cast<int>(i - r * pieces);
+  const int src = sorted_rows[r];
+  out[i] = src < 0 ? make_uint4(0, 0, 0, 0) : x[static_cast<long long>(src) * pieces + c];
+}
+__global__ void relu2_kernel(__nv_bfloat162* p, long long n2) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n2) return;
+  float2 v = __bfloat1622float2(p[i]);
+  v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f);
+  p[i] = __floats2bfloat162_rn(v.x * v.x, v.y * v.y);
+}
+}  // namespace
+
+int moe_gather_bf16(const void* x, const int* sorted_rows, void* out, int rows, int W, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (W % 8) return -1;
+  const long long total = static_cast<long long>(rows) * (W / 8);
+  moe_gather_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(static_cast<const uint4*>(x), sorted_rows, static_cast<uint4*>(out), W / 8, total);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int relu2_bf16(void* p, long long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n % 2) return -1;
+  relu2_kernel<<<static_cast<unsigned>((n / 2 + 255) / 256), 256, 0, st>>>(static_cast<__nv_bfloat162*>(p), n / 2);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

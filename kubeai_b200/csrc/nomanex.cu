@@ -69,6 +69,7 @@ struct LayerWeights {
   void* e_up = nullptr;    // [experts][ff][width]
   void* e_down = nullptr;  // [experts][width][ff]
   GemmPlan p_in, p_out;    // tcgen05 projections (bf16 storage, K % 8 == 0)
+  std::vector<GemmPlan> p_eup, p_edown;   // per expert, for steps large enough to pay for a count read-back
   CUtensorMap xm_out[kGemmNumBlockN];   // activation maps over the output projection's input [Tcap, k_out]
   bool tc_in = false, tc_out = false;
 };
@@ -106,6 +107,8 @@ class Nomanex : public Model {
         *logits = nullptr;
   int *topi = nullptr, *sorted_rows = nullptr, *tile_group = nullptr, *pair_pos = nullptr;
   int row_cap = 0, moe_cap = 0;
+  void *hsorted = nullptr, *edown16 = nullptr;   // per-expert tensor-core path: gathered inputs, bf16 expert outputs
+  int *expert_rows = nullptr, *expert_rows_host = nullptr;
   std::vector<void*> allocs;
   // tcgen05 projections
   float* gemm_ws = nullptr;
@@ -119,8 +122,10 @@ class Nomanex : public Model {
       if (w.tc_in) gemm_plan_destroy(&w.p_in);
       if (w.tc_out) gemm_plan_destroy(&w.p_out);
     }
+    if (expert_rows_host) cudaFreeHost(expert_rows_host);
     for (void* p : allocs) cudaFree(p);
   }
+  // (profiling events are released with the context)
   const char* arch() const override { return "Nomanex"; }
   int vocab() const override { return V; }
 
@@ -371,6 +376,24 @@ class Nomanex : public Model {
       for (int j = 0; j < kGemmNumBlockN && w.tc_out; ++j)
         if (gemm_make_x_map(&w.xm_out[j], ycat, env.Tcap, s.k_out, s.k_out, bns[j])) w.tc_out = false;
       if (w.tc_out) w.p_out.ws_bytes = ws_bytes;
+      if (s.ff_kind == FF_MOE && s.ff % 8 == 0) {
+        w.p_eup.resize(s.experts);
+        w.p_edown.resize(s.experts);
+        bool ok = true;
+        for (int e = 0; e < s.experts && ok; ++e) {
+          ok = gemm_plan_init(&w.p_eup[e], static_cast<bf16*>(w.e_up) + static_cast<size_t>(e) * s.ff * W, s.ff, W, W, gemm_ws, gemm_counters, env.sms) == 0 &&
+               gemm_plan_init(&w.p_edown[e], static_cast<bf16*>(w.e_down) + static_cast<size_t>(e) * W * s.ff, W, s.ff, s.ff, gemm_ws, gemm_counters, env.sms) == 0;
+          w.p_eup[e].ws_bytes = w.p_edown[e].ws_bytes = ws_bytes;
+        }
+        if (!ok) { w.p_eup.clear(); w.p_edown.clear(); }
+      }
+    }
+    if (moe_cap) {
+      int max_e = 1;
+      for (auto& s : spec) max_e = std::max(max_e, s.experts);
+      if (dalloc(&hsorted, static_cast<size_t>(moe_cap) * W * 2) || dalloc(&edown16, static_cast<size_t>(moe_cap) * W * 2) ||
+          dalloc(&expert_rows, static_cast<size_t>(max_e) * 2 * sizeof(int))) return -3;
+      if (cudaMallocHost(&expert_rows_host, static_cast<size_t>(max_e) * 2 * sizeof(int)) != cudaSuccess) return -3;
     }
     return 0;
   }
@@ -520,42 +543,64 @@ class Nomanex : public Model {
 
   // ------------------------------------------------------------ forward
   int project(const GemmPlan& plan, bool tc, const CUtensorMap* xm, const void* X, const void* Wm, void* Y, int T, int N, int K) {
-    if (tc && T > 8) {
+    static const int tc_min_t = [] { const char* e = getenv("B200_NX_TC_MIN_T"); return e ? atoi(e) : 1; }();   // A/B knob
+    if (tc && T >= tc_min_t) {
       const int bn = gemm_block_n_for(T);
       return gemm_run(plan, xm[gemm_block_n_index(bn)], bn, Y, N, T, env.stream);
     }
     return linear(linear_args(X, dt, Wm, dt, Y, dt, T, N, K), env.stream);
   }
 
+  // per-kernel device time (b200_engine_kernel_times): with profiling on, every launch is bracketed by events and waited for
+  cudaEvent_t pe0 = nullptr, pe1 = nullptr;
+  void prof_start() {
+    if (!profile_kernels) return;
+    if (!pe0) { cudaEventCreate(&pe0); cudaEventCreate(&pe1); }
+    cudaEventRecord(pe0, env.stream);
+  }
+  void prof_stop(const char* name) {
+    if (!profile_kernels) return;
+    cudaEventRecord(pe1, env.stream);
+    cudaEventSynchronize(pe1);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, pe0, pe1);
+    auto& t = kernel_times[name];
+    t.first += ms * 1000.0;
+    t.second += 1;
+  }
+#define KRN(name, call) do { prof_start(); const int r_ = (call); if (r_ && !rc) { failed_kernel = name; failed_rc = r_; } rc |= r_; prof_stop(name); } while (0)
+  const char* failed_kernel = "";
+  int failed_rc = 0;
+
   int forward(const StepBatch& b, int* sampled, float* host_logits, int64_t* launches) override {
     cudaStream_t st = env.stream;
     const int T = b.T;
     int rc = 0;
     int64_t nl = 0;
-    rc |= embed_bigram(embed, bigram, dt, b.ids, b.prev_ids, x, T, W, V, buckets, mul_prev, mul_cur, st);
+    KRN("embed", embed_bigram(embed, bigram, dt, b.ids, b.prev_ids, x, T, W, V, buckets, mul_prev, mul_cur, st));
     const LayerWeights& w0 = wts[spec[0].weights_of];
-    rc |= residual_dyt(x, nullptr, nullptr, dt, 0.f, w0.norm_w, w0.norm_b, w0.norm_alpha, h, dt, nullptr, T, W, st);
+    KRN("residual_norm", residual_dyt(x, nullptr, nullptr, dt, 0.f, w0.norm_w, w0.norm_b, w0.norm_alpha, h, dt, nullptr, T, W, st));
     nl += 2;
     for (size_t li = 0; li < spec.size() && !rc; ++li) {
       const LayerSpec& s = spec[li];
       const LayerWeights& w = wts[s.weights_of];
       const LayerRun& r = run[li];
       const int HV = s.heads * s.vdim;
-      rc |= project(w.p_in, w.tc_in, xm_h, h, w.w_in, inb, T, s.n_in, W);
+      KRN("proj_in", project(w.p_in, w.tc_in, xm_h, h, w.w_in, inb, T, s.n_in, W));
       ++nl;
       const size_t es = dtype_bytes(dt);
       auto col = [&](void* base, size_t off) { return static_cast<void*>(static_cast<uint8_t*>(base) + off * es); };
       if (s.mixer == MIX_GLA) {
         LinearArgs la = linear_args(col(inb, s.off_a1), dt, w.a2, dt, z, DT_F32, T, s.heads * s.dim, s.a_rank);
         la.ldx = s.n_in;
-        rc |= linear(la, st);
+        KRN("gla_decay_proj", linear(la, st));
         GlaArgs g;
         g.qkv = inb; g.t = dt; g.ld = s.n_in; g.q_off = s.off_q; g.k_off = s.off_k; g.v_off = s.off_v;
         g.z = z; g.z_bias = w.a2_b; g.inv_tau = 1.0f / s.tau; g.q_scale = 1.0f / sqrtf(static_cast<float>(s.dim));
         g.states = r.state; g.seqs = b.seqs; g.nseq = b.nseq;
         g.heads = s.heads; g.dim = s.dim; g.vdim = s.vdim; g.o = o32;
-        rc |= gla_scan(g, st);
-        rc |= gla_out_gate(o32, col(inb, s.off_g), s.n_in, w.o_norm, eps, ycat, s.k_out, dt, T, s.heads, s.vdim, st);
+        KRN("gla_scan", gla_scan(g, st));
+        KRN("gla_out_gate", gla_out_gate(o32, col(inb, s.off_g), s.n_in, w.o_norm, eps, ycat, s.k_out, dt, T, s.heads, s.vdim, st));
         nl += 3;
       } else {
         const int C = s.kv_rank, R = s.rot_dim, E = C + R;
@@ -564,49 +609,87 @@ class Nomanex : public Model {
         p.norm_w = w.c_norm; p.eps = eps; p.rope = w.rope; p.rot_dims = s.rot_dims;
         p.positions = b.pos; p.slots = b.slots; p.cache = r.cache; p.qlat = qlat;
         p.T = T; p.heads = s.heads; p.dim = s.dim; p.rot_dim = R; p.kv_rank = C;
-        rc |= latent_prep(p, st);
+        KRN("latent_prep", latent_prep(p, st));
         // latent query: per head [T, dim] x [kv_rank, dim]^T into the head's first kv_rank columns of qlat
         LinearArgs lq = linear_args(col(inb, s.off_q), dt, w.uk_t, dt, qlat, DT_F32, T, C, s.dim);
         lq.ldx = s.n_in; lq.ldy = s.heads * E; lq.batch = s.heads; lq.xbs = s.dim + R; lq.wbs = static_cast<long long>(C) * s.dim; lq.ybs = E;
-        rc |= linear(lq, st);
+        KRN("latent_q_absorb", linear(lq, st));
         LatentAttnArgs a;
         a.qlat = qlat; a.cache = r.cache; a.t = dt; a.positions = b.pos; a.seq_of_tok = b.seq_of_tok; a.block_tables = b.btab;
         a.max_blocks = b.max_blocks; a.page = env.page; a.olat = olat;
         a.T = T; a.heads = s.heads; a.kv_rank = C; a.rot_dim = R; a.window = std::min(s.window, env.max_model_len); a.scale = s.scale;
-        rc |= latent_attention(a, st);
+        a.seqs = b.seqs; a.nseq = b.nseq;
+        KRN("latent_attention", latent_attention(a, st));
         // values: per head [T, kv_rank] x [vdim, kv_rank]^T into the head's columns of the output projection's input
         LinearArgs lv = linear_args(olat, DT_F32, w.uv, dt, ycat, dt, T, s.vdim, C);
         lv.ldx = s.heads * C; lv.ldy = s.k_out; lv.batch = s.heads; lv.xbs = C; lv.wbs = static_cast<long long>(s.vdim) * C; lv.ybs = s.vdim;
-        rc |= linear(lv, st);
-        rc |= sigmoid_gate(ycat, s.k_out, col(inb, s.off_g), s.n_in, dt, T, HV, st);
+        KRN("latent_v_expand", linear(lv, st));
+        KRN("sigmoid_gate", sigmoid_gate(ycat, s.k_out, col(inb, s.off_g), s.n_in, dt, T, HV, st));
         nl += 5;
       }
       if (s.ff_kind == FF_DENSE) {
-        rc |= glu_clamped(col(inb, s.off_gu), s.n_in, col(ycat, HV), s.k_out, dt, T, s.ff, s.limit, 1.702f, st);
+        KRN("glu", glu_clamped(col(inb, s.off_gu), s.n_in, col(ycat, HV), s.k_out, dt, T, s.ff, s.limit, 1.702f, st));
         ++nl;
       }
-      rc |= project(w.p_out, w.tc_out, w.xm_out, ycat, w.w_out, ao, T, W, s.k_out);
+      KRN("proj_out", project(w.p_out, w.tc_out, w.xm_out, ycat, w.w_out, ao, T, W, s.k_out));
       ++nl;
       const void* f_out = nullptr;
       if (s.ff_kind == FF_MOE) {
-        rc |= linear(linear_args(h, dt, w.router, dt, scores, DT_F32, T, s.experts, W), st);
-        rc |= moe_route(scores, topi, topw, T, s.experts, s.groups, s.keep, s.top, st);
+        KRN("moe_router", linear(linear_args(h, dt, w.router, dt, scores, DT_F32, T, s.experts, W), st));
+        KRN("moe_route", moe_route(scores, topi, topw, T, s.experts, s.groups, s.keep, s.top, st));
         const int cap = (T * s.top + 63) / 64 * 64 + s.experts * 64;
-        rc |= moe_align(topi, T, s.top, s.experts, sorted_rows, tile_group, pair_pos, cap, st);
-        LinearArgs up = linear_args(h, dt, w.e_up, dt, eact, dt, cap, s.ff, W);
-        up.x_rows = sorted_rows; up.tile_group = tile_group; up.wbs = static_cast<long long>(s.ff) * W; up.act = LIN_RELU2;
-        rc |= linear(up, st);
-        LinearArgs dn = linear_args(eact, dt, w.e_down, dt, edown, DT_F32, cap, W, s.ff);
-        dn.tile_group = tile_group; dn.wbs = static_cast<long long>(W) * s.ff;
-        rc |= linear(dn, st);
-        rc |= moe_combine(edown, pair_pos, topw, fo, dt, T, s.top, W, st);
+        const char* mte = getenv("B200_NX_MOE_TC_MIN_T");   // A/B knob
+        const int moe_tc_min = mte ? atoi(mte) : 256;
+        const bool per_expert = !w.p_eup.empty() && T >= moe_tc_min;
+        KRN("moe_align", moe_align(topi, T, s.top, s.experts, sorted_rows, tile_group, pair_pos, cap, st, per_expert ? expert_rows : nullptr));
+        if (per_expert) {
+          // Large steps: every expert's rows are one tcgen05 GEMM.  The row counts come back to the host (one small copy
+          // and a wait per layer, paid only by steps of hundreds of tokens), the inputs are gathered into sorted order.
+          KRN("moe_gather", moe_gather_bf16(h, sorted_rows, hsorted, cap, W, st));
+          if (cudaMemcpyAsync(expert_rows_host, expert_rows, static_cast<size_t>(s.experts) * 2 * sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+              cudaStreamSynchronize(st) != cudaSuccess) rc = -2;
+          prof_start();
+          for (int e = 0; e < s.experts && !rc; ++e) {
+            const int start = expert_rows_host[2 * e], cnt = expert_rows_host[2 * e + 1];
+            if (cnt <= 0) continue;
+            const int bn = gemm_block_n_for(cnt);
+            CUtensorMap tm;
+            if (gemm_make_x_map(&tm, static_cast<bf16*>(hsorted) + static_cast<size_t>(start) * W, cnt, W, W, bn)) { rc = -2; break; }
+            rc |= gemm_run(w.p_eup[e], tm, bn, static_cast<bf16*>(eact) + static_cast<size_t>(start) * s.ff, s.ff, cnt, st);
+            ++nl;
+          }
+          prof_stop("moe_up");
+          KRN("moe_act", relu2_bf16(eact, static_cast<long long>(cap) * s.ff, st));
+          prof_start();
+          for (int e = 0; e < s.experts && !rc; ++e) {
+            const int start = expert_rows_host[2 * e], cnt = expert_rows_host[2 * e + 1];
+            if (cnt <= 0) continue;
+            const int bn = gemm_block_n_for(cnt);
+            CUtensorMap tm;
+            if (gemm_make_x_map(&tm, static_cast<bf16*>(eact) + static_cast<size_t>(start) * s.ff, cnt, s.ff, s.ff, bn)) { rc = -2; break; }
+            rc |= gemm_run(w.p_edown[e], tm, bn, static_cast<bf16*>(edown16) + static_cast<size_t>(start) * W, W, cnt, st);
+            ++nl;
+          }
+          prof_stop("moe_down");
+          KRN("moe_combine", moe_combine(edown16, DT_BF16, pair_pos, topw, fo, dt, T, s.top, W, st));
+          nl += 5;
+        } else {
+          LinearArgs up = linear_args(h, dt, w.e_up, dt, eact, dt, cap, s.ff, W);
+          up.x_rows = sorted_rows; up.tile_group = tile_group; up.wbs = static_cast<long long>(s.ff) * W; up.act = LIN_RELU2;
+          KRN("moe_up", linear(up, st));
+          LinearArgs dn = linear_args(eact, dt, w.e_down, dt, edown, DT_F32, cap, W, s.ff);
+          dn.tile_group = tile_group; dn.wbs = static_cast<long long>(W) * s.ff;
+          KRN("moe_down", linear(dn, st));
+          KRN("moe_combine", moe_combine(edown, DT_F32, pair_pos, topw, fo, dt, T, s.top, W, st));
+          nl += 4;
+        }
         f_out = fo;
-        nl += 6;
+        nl += 2;
       }
       const bool last = li + 1 == spec.size();
       const LayerWeights* nw = last ? nullptr : &wts[spec[li + 1].weights_of];
-      rc |= residual_dyt(x, ao, f_out, dt, mult, nw ? nw->norm_w : nullptr, nw ? nw->norm_b : nullptr, nw ? nw->norm_alpha : nullptr,
-                         last ? nullptr : h, dt, nullptr, T, W, st);
+      KRN("residual_norm", residual_dyt(x, ao, f_out, dt, mult, nw ? nw->norm_w : nullptr, nw ? nw->norm_b : nullptr, nw ? nw->norm_alpha : nullptr,
+                         last ? nullptr : h, dt, nullptr, T, W, st));
       ++nl;
       if (residual_sink && !rc) {
         const size_t at = residual_sink->size();
@@ -618,20 +701,22 @@ class Nomanex : public Model {
     // head: final norm of the wanted rows, logits in fp32, greedy choice; in chunks of row_cap rows
     for (int r0 = 0; r0 < b.S && !rc; r0 += row_cap) {
       const int n = std::min(row_cap, b.S - r0);
-      rc |= residual_dyt(x, nullptr, nullptr, dt, 0.f, fin_w, fin_b, fin_alpha, hrow, dt, b.rows + r0, n, W, st);
-      rc |= linear(linear_args(hrow, dt, head, dt, logits, DT_F32, n, V, W), st);
-      rc |= argmax_f32(logits, sampled + r0, n, V, st);
+      KRN("residual_norm", residual_dyt(x, nullptr, nullptr, dt, 0.f, fin_w, fin_b, fin_alpha, hrow, dt, b.rows + r0, n, W, st));
+      KRN("head", linear(linear_args(hrow, dt, head, dt, logits, DT_F32, n, V, W), st));
+      KRN("argmax", argmax_f32(logits, sampled + r0, n, V, st));
       nl += 3;
       if (host_logits && cudaMemcpyAsync(host_logits + static_cast<size_t>(r0) * V, logits, static_cast<size_t>(n) * V * sizeof(float),
                                          cudaMemcpyDeviceToHost, st) != cudaSuccess) rc = -2;
     }
     if (launches) *launches += nl;
-    if (rc) { set_error("Nomanex forward: a kernel launch failed (%s)", cudaGetErrorString(cudaGetLastError())); return -2; }
+    if (rc) { set_error("Nomanex forward: %s failed with %d (%s)", failed_kernel, failed_rc, cudaGetErrorString(cudaGetLastError())); return -2; }
     return 0;
   }
 };
 
 }  // namespace
+
+#undef KRN
 
 std::unique_ptr<Model> make_nomanex(const JVal& config, DType dtype, std::string* err) {
   std::unique_ptr<Nomanex> m(new Nomanex(dtype));

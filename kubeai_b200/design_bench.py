@@ -1,0 +1,168 @@
+"""Prefill and decode throughput of a registered design beside the built-in Llama model at equal width, depth and
+feed-forward size, on random weights (`bench.py --design nomanex`).  Every number is CUDA-event time of the engine's
+own step (b200_feed_step: the same packing, page pool, state slots and kernels as a scheduled step), after warm-up
+steps, with a buffer larger than L2 written between timed steps.  Per-kernel times come from a separate pass in which
+each launch is bracketed by events (b200_engine_profile_kernels for the design, b200_engine_profile_range for Llama),
+and are turned into fractions of the measured bf16 / HBM peaks from the kernels' algorithmic FLOPs and bytes."""
+from __future__ import annotations
+
+import json
+import os
+import tempfile
+
+import numpy as np
+
+SIZES = {
+    # name: width, latent/gla heads, dense ff, experts x expert ff (top, groups, keep), window, layers of each kind
+    "w2048": dict(width=2048, heads=16, ff=8192, experts=16, eff=2048, top=2, groups=4, keep=2, window=1024, vocab=32000),
+    "w4096": dict(width=4096, heads=32, ff=14336, experts=16, eff=4096, top=2, groups=4, keep=2, window=2048, vocab=32000),
+}
+DIM, ROT, VDIM, RANK = 128, 64, 128, 512
+
+
+def nomanex_config(z):
+    lat = dict(heads=z["heads"], dim=DIM, rot_dim=ROT, vdim=VDIM, kv_rank=RANK, mask=dict(size=z["window"]),
+               rot=dict(base=10000.0, dims=ROT), scale=(DIM + ROT) ** -0.5)
+    gl = dict(heads=z["heads"], dim=DIM, vdim=VDIM, tau=16.0)
+    dn = dict(kind="dense", ff=z["ff"], limit=7.0)
+    mo = dict(kind="moe", expert=dict(ff=z["eff"]), router=dict(experts=z["experts"], top=z["top"], groups=dict(count=z["groups"], keep=z["keep"])))
+    layers = [dict(type="latent_attention", mixer=lat, mlp=dn), dict(type="gla", mixer=gl, mlp=mo),
+              dict(type="gla", mixer=gl, mlp=dn), dict(type="latent_attention", mixer=lat, mlp=mo)]
+    return dict(architecture="Nomanex", vocab=z["vocab"], width=z["width"], residual_mult=0.5, norm=dict(eps=1e-5),
+                embedding=dict(bigram=dict(buckets=65521, mul_prev=127, mul_cur=17)), layers=layers)
+
+
+def flush_l2(torch, buf):
+    buf.add_(1)
+    torch.cuda.synchronize()
+
+
+def run_engine(e, torch, buf, vocab, batch, prompt, decode_steps, warmup):
+    rng = np.random.default_rng(0)
+    out = {}
+    # prefill: `batch` prompts of `prompt` tokens in one step
+    times = []
+    for it in range(warmup + 3):
+        rids = [e.feed_open() for _ in range(batch)]
+        flush_l2(torch, buf)
+        e.feed_step([(r, rng.integers(0, vocab, size=prompt).tolist(), [prompt - 1]) for r in rids])
+        times.append(e.stats().last_step_device_us)
+        if it < warmup + 2:
+            for r in rids:
+                e.feed_close(r)
+    us = float(np.median(times[warmup:]))
+    out["prefill"] = dict(tokens=batch * prompt, step_ms=us / 1e3, tok_s=batch * prompt / us * 1e6)
+    # decode: the last batch stays live; one token per sequence per step
+    times = []
+    for it in range(warmup + decode_steps):
+        flush_l2(torch, buf)
+        e.feed_step([(r, [int(rng.integers(0, vocab))], [0]) for r in rids])
+        times.append(e.stats().last_step_device_us)
+    us = float(np.median(times[warmup:]))
+    out["decode"] = dict(seqs=batch, context=prompt + warmup, step_ms=us / 1e3, tok_s=batch / us * 1e6)
+    return out, rids
+
+
+def bench_size(name, z, batch, prompt, decode_steps, warmup, peaks):
+    import torch
+    from .engine import Engine, default_config
+    hbm, tf, _ = peaks
+    buf = torch.zeros(160 << 20, dtype=torch.int16, device="cuda")   # 320 MB > 126 MB of L2
+    lim = dict(manual_step=1, enable_prefix_caching=0, max_num_seqs=batch, max_batched_tokens=batch * prompt,
+               max_model_len=prompt + warmup + decode_steps + 64, record_steps=4, seed=1)
+    lim["num_kv_blocks"] = batch * ((lim["max_model_len"] + 15) // 16)
+    res = {"size": dict(z, batch=batch, prompt=prompt)}
+    cfgj = nomanex_config(z)
+    T = batch * prompt
+    with tempfile.TemporaryDirectory() as d:
+        with open(os.path.join(d, "config.json"), "w") as f:
+            json.dump(cfgj, f)
+        with Engine(default_config(**lim), d, dtype="bfloat16", random_weights=True) as e:
+            r, rids = run_engine(e, torch, buf, z["vocab"], batch, prompt, decode_steps, warmup)
+            # per-kernel pass: one prefill step of the same shape, then one decode step
+            for q in rids:
+                e.feed_close(q)
+            rng = np.random.default_rng(1)
+            rids = [e.feed_open() for _ in range(batch)]
+            e.profile_kernels(True)
+            e.feed_step([(q, rng.integers(0, z["vocab"], size=prompt).tolist(), [prompt - 1]) for q in rids])
+            kp = e.kernel_times()
+            e.profile_kernels(True)
+            e.feed_step([(q, [1], [0]) for q in rids])
+            kd = e.kernel_times()
+            e.profile_kernels(False)
+            r["kernels_prefill_us"] = {k: round(v["us"], 1) for k, v in sorted(kp.items())}
+            r["kernels_decode_us"] = {k: round(v["us"], 1) for k, v in sorted(kd.items())}
+            # algorithmic work of the two mixers and of the projections (per step, both layers of a kind together)
+            H, E, W = z["heads"], RANK + ROT, z["width"]
+            keys = sum(min(p + 1, z["window"]) for p in range(prompt)) * batch
+            att_flops = 2.0 * 2 * H * keys * (E + RANK)
+            gla_flops = 2.0 * 3 * 2 * T * H * DIM * VDIM
+            n_in = sum(_n_in(ly, W) for ly in cfgj["layers"])
+            k_out = sum(_k_out(ly) for ly in cfgj["layers"])
+            proj_flops = 2.0 * T * W * (n_in + k_out)
+            state_bytes = 2.0 * 2 * batch * H * DIM * VDIM * 4
+            dkeys = batch * min(prompt + 1, z["window"])
+            r["roofline"] = {
+                "latent_attention_prefill_frac_of_bf16_peak": att_flops / (kp["latent_attention"]["us"] * 1e-6) / (tf * 1e12),
+                "gla_scan_prefill_tflops": gla_flops / (kp["gla_scan"]["us"] * 1e-6) / 1e12,
+                "projections_prefill_frac_of_bf16_peak": proj_flops / ((kp["proj_in"]["us"] + kp["proj_out"]["us"]) * 1e-6) / (tf * 1e12),
+                "gla_scan_decode_frac_of_hbm": state_bytes / (kd["gla_scan"]["us"] * 1e-6) / (hbm * 1e9),
+                "latent_attention_decode_frac_of_hbm": 2.0 * dkeys * E * 2 / (kd["latent_attention"]["us"] * 1e-6) / (hbm * 1e9),
+                "projections_decode_frac_of_hbm": 2.0 * W * (n_in + k_out) / ((kd["proj_in"]["us"] + kd["proj_out"]["us"]) * 1e-6) / (hbm * 1e9),
+            }
+        res["nomanex"] = r
+    # the closest existing model: Llama at equal width, depth, heads x 128 and feed-forward size
+    lcfg = default_config(num_layers=4, hidden=z["width"], q_heads=z["heads"], kv_heads=z["heads"] // 4, intermediate=z["ff"],
+                          vocab=z["vocab"], **lim)
+    with Engine(lcfg) as e:
+        r, rids = run_engine(e, torch, buf, z["vocab"], batch, prompt, decode_steps, warmup)
+        cls, tot = e.profile_range(1, 1, batch)            # the last decode step
+        r["kernels_decode_us"] = {k: round(v["us"], 1) for k, v in cls.items() if v["launches"]}
+        for q in rids:
+            e.feed_close(q)
+        rng = np.random.default_rng(1)
+        rids = [e.feed_open() for _ in range(batch)]
+        e.feed_step([(q, rng.integers(0, z["vocab"], size=prompt).tolist(), [prompt - 1]) for q in rids])
+        cls, tot = e.profile_range(1, batch + 1, 1 << 30)
+        r["kernels_prefill_us"] = {k: round(v["us"], 1) for k, v in cls.items() if v["launches"]}
+        Hq, Wd, I = z["heads"], z["width"], z["ff"]
+        keys = sum(p + 1 for p in range(prompt)) * batch
+        att_flops = 4.0 * 4 * Hq * 128 * keys
+        pj = [k for k in ("gemm_qkv", "gemm_o", "gemm_gate_up", "gemm_down") if k in r["kernels_prefill_us"]]
+        proj_flops = 2.0 * T * 4 * (Wd * (Hq + Hq // 2) * 128 + Wd * Hq * 128 + 3 * Wd * I)
+        dk = r["kernels_decode_us"]
+        r["roofline"] = {
+            "attention_prefill_frac_of_bf16_peak": att_flops / (r["kernels_prefill_us"]["attn_prefill"] * 1e-6) / (tf * 1e12),
+            "projections_prefill_frac_of_bf16_peak": proj_flops / (sum(r["kernels_prefill_us"][k] for k in pj) * 1e-6) / (tf * 1e12),
+            "attention_decode_frac_of_hbm": 4.0 * batch * (prompt + warmup + decode_steps) * (Hq // 4) * 128 * 2 * 2 / (dk["attn_decode"] * 1e-6) / (hbm * 1e9),
+            "projections_decode_frac_of_hbm": 2.0 * 4 * (Wd * (Hq + Hq // 2) * 128 + Wd * Hq * 128 + 3 * Wd * I) /
+                                              (sum(dk[k] for k in ("gemm_qkv", "gemm_o", "gemm_gate_up", "gemm_down") if k in dk) * 1e-6) / (hbm * 1e9),
+        }
+        res["llama"] = r
+    del buf
+    return res
+
+
+def _n_in(ly, W):
+    mx = ly["mixer"]
+    if ly["type"] == "gla":
+        n = 2 * mx["heads"] * mx["dim"] + 2 * mx["heads"] * mx["vdim"] + 16
+    else:
+        n = mx["heads"] * (mx["dim"] + mx["rot_dim"]) + mx["kv_rank"] + mx["rot_dim"] + mx["heads"] * mx["vdim"]
+    return n + (2 * ly["mlp"]["ff"] if ly["mlp"]["kind"] == "dense" else 0)
+
+
+def _k_out(ly):
+    return ly["mixer"]["heads"] * ly["mixer"]["vdim"] + (ly["mlp"]["ff"] if ly["mlp"]["kind"] == "dense" else 0)
+
+
+def run(design, peaks, sizes=None, batch=8, prompt=512, decode_steps=8, warmup=3):
+    if design != "nomanex":
+        raise SystemExit("unknown design %r (known: nomanex)" % design)
+    out = {"design": design, "dtype": "bf16", "data": "synthetic (seeded random weights and tokens)", "peaks": dict(hbm_gbs=peaks[0], bf16_tflops=peaks[1], source=peaks[2]),
+           "timing": "CUDA events around the engine step, median of the timed steps, %d warm-up steps, 320 MB written between steps" % warmup,
+           "sizes": {}}
+    for name in sizes or list(SIZES):
+        out["sizes"][name] = bench_size(name, SIZES[name], batch, prompt, decode_steps, warmup, peaks)
+    return out

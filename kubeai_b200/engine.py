@@ -233,6 +233,16 @@ class Engine:
         check(self._l.b200_feed_step(self._h, arr, len(entries), out.ctypes.data_as(C.POINTER(C.c_float)), out.size))
         return out
 
+    def profile_kernels(self, on: bool):
+        check(self._l.b200_engine_profile_kernels(self._h, 1 if on else 0))
+
+    def kernel_times(self) -> dict:
+        import json
+        n = check(self._l.b200_engine_kernel_times(self._h, None, 0))
+        buf = C.create_string_buffer(n + 1)
+        self._l.b200_engine_kernel_times(self._h, buf, n + 1)
+        return json.loads(buf.value)
+
     def debug_residuals(self, on: bool):
         check(self._l.b200_engine_debug_residuals(self._h, 1 if on else 0))
 

@@ -100,6 +100,44 @@ def test_bfloat16_widths_the_tensor_core_projection_cannot_take(tmp_path):
         close32(feed_whole(e, t), want)
 
 
+@pytest.mark.parametrize("heads,kv_rank,rot_dim,window", [(2, 16, 16, 100), (16, 48, 16, 70), (20, 32, 32, 33), (3, 16, 16, 500)])
+def test_bfloat16_tensor_core_attention_equals_the_plain_kernel(tmp_path, monkeypatch, heads, kv_rank, rot_dim, window):
+    """Latent widths that fit the mma fragments take the tensor-core attention kernel: several 64-key tiles per window,
+    several tokens per 16-row tile (few heads), several head groups (more than 16 heads), portions and decoding."""
+    layers = [(latent(heads=heads, dim=8, rot_dim=rot_dim, vdim=8, kv_rank=kv_rank, window=window), None)]
+    cfg, W, d = build(tmp_path, layers, seed=21, q_gain=3.0, width=32)
+    t = toks(230, cfg["vocab"], 22)
+    want = oracle_for(cfg, W).forward(t)
+    with open_engine(d, dtype="bfloat16") as e:
+        whole = feed_whole(e, t)
+        cut = feed_portions(e, t, [67, 2, 90, 1])
+    monkeypatch.setenv("B200_NX_ATTN_MMA", "0")
+    with open_engine(d, dtype="bfloat16") as e:
+        plain = feed_whole(e, t)
+    close16(whole, want)
+    close16(cut, want)
+    assert np.median(rel_err(whole, plain)) < 0.02 and np.median(rel_err(cut, plain)) < 0.02
+    assert rel_err(whole, plain).max() < 0.1 and rel_err(cut, plain).max() < 0.1
+
+
+def test_bfloat16_per_expert_tensor_core_path_equals_the_grouped_kernel(tmp_path, monkeypatch):
+    """Large steps run every expert's rows as one tensor-core GEMM after reading the row counts back; forced here for
+    small steps, including experts that get no token at all."""
+    cfg, W, d = build(tmp_path, [(gla(), moe(experts=12, top=3, count=4, keep=2, ff=16)), (latent(), moe(experts=4, top=1, count=1, keep=1, ff=8))],
+                      seed=31, width=32)
+    t = toks(150, cfg["vocab"], 32)
+    want = oracle_for(cfg, W).forward(t)
+    with open_engine(d, dtype="bfloat16") as e:
+        grouped = feed_whole(e, t)
+    monkeypatch.setenv("B200_NX_MOE_TC_MIN_T", "1")
+    with open_engine(d, dtype="bfloat16") as e:
+        per_expert = feed_whole(e, t)
+        cut = feed_portions(e, t, [3, 70, 1])
+    close16(per_expert, want)
+    close16(cut, want)
+    assert np.median(rel_err(per_expert, grouped)) < 0.03
+
+
 # ---------------------------------------------------------------- prefill, decoding, portions
 def test_prefill_equals_token_by_token_decoding(mix):
     cfg, W, d, o = mix
