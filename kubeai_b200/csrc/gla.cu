@@ -30,28 +30,34 @@ constexpr int kThreads = 128;
 // (rows past dim are zeros; the 4-float pad puts the P slices a thread group reads at once into different banks, and a
 // thread reads its slice as float4), then v and o for the CTA's columns [G][cols] each, so the sequential token loop
 // touches shared memory only.
-template <typename T>
+// NC = value columns per thread (2 when the value width keeps every SM busy with half as many CTAs: each q, k, alpha read
+// from shared memory then feeds twice the arithmetic).
+template <typename T, int NC>
 __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, int rpp, int G) {
   extern __shared__ __align__(16) float sm[];
   const int seq = blockIdx.z, head = blockIdx.y;
   const int tok0 = a.seqs[seq * 8 + 0], n = a.seqs[seq * 8 + 1], pos0 = a.seqs[seq * 8 + 2], slot = a.seqs[seq * 8 + 3];
   const int D = a.dim, Dv = a.vdim;
   const int part = threadIdx.x % P, jj = threadIdx.x / P;
-  const int cols = kThreads / P;
-  const int j = blockIdx.x * cols + jj;
-  const bool live = j < Dv;
+  const int tcols = kThreads / P, cols = tcols * NC;   // columns per thread group, per CTA
+  int j[NC];
+  bool live[NC];
+#pragma unroll
+  for (int c = 0; c < NC; ++c) { j[c] = blockIdx.x * cols + jj + c * tcols; live[c] = j[c] < Dv; }
   const int i0 = part * rpp;
   const int ps = rpp + 4, Dp = P * ps;     // padded slice and row length
   float* vs = sm + static_cast<size_t>(G) * 3 * Dp;
   float* os = vs + G * cols;
   const T* base = static_cast<const T*>(a.qkv);
   float* Sg = a.states + ((static_cast<long long>(slot) * a.heads + head) * D) * Dv;
-  float S[kRows];
+  float S[NC][kRows];
 #pragma unroll
-  for (int r = 0; r < kRows; ++r) {
-    const int i = i0 + r;
-    S[r] = (live && r < rpp && i < D && pos0 > 0) ? Sg[static_cast<long long>(i) * Dv + j] : 0.f;
-  }
+  for (int c = 0; c < NC; ++c)
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      const int i = i0 + r;
+      S[c][r] = (live[c] && r < rpp && i < D && pos0 > 0) ? Sg[static_cast<long long>(i) * Dv + j[c]] : 0.f;
+    }
   const int slice_elems = P * rpp;
   for (int g0 = 0; g0 < n; g0 += G) {
     const int gn = min(G, n - g0);
@@ -81,24 +87,32 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
     }
     __syncthreads();
     for (int tt = 0; tt < gn; ++tt) {
-      const float v = vs[tt * cols + jj];
+      float v[NC], o[NC][4];
+#pragma unroll
+      for (int c = 0; c < NC; ++c) { v[c] = vs[tt * cols + jj + c * tcols]; o[c][0] = o[c][1] = o[c][2] = o[c][3] = 0.f; }
       const float4* q4 = reinterpret_cast<const float4*>(sm + (tt * 3) * Dp + part * ps);
       const float4* k4 = reinterpret_cast<const float4*>(sm + (tt * 3 + 1) * Dp + part * ps);
       const float4* a4 = reinterpret_cast<const float4*>(sm + (tt * 3 + 2) * Dp + part * ps);
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
       for (int m = 0; m < kRows / 4; ++m) {
         if (4 * m < rpp) {
           const float4 qa = q4[m], ka = k4[m], aa = a4[m];
-          S[4 * m] = fmaf(aa.x, S[4 * m], ka.x * v);         o0 = fmaf(S[4 * m], qa.x, o0);
-          S[4 * m + 1] = fmaf(aa.y, S[4 * m + 1], ka.y * v); o1 = fmaf(S[4 * m + 1], qa.y, o1);
-          S[4 * m + 2] = fmaf(aa.z, S[4 * m + 2], ka.z * v); o2 = fmaf(S[4 * m + 2], qa.z, o2);
-          S[4 * m + 3] = fmaf(aa.w, S[4 * m + 3], ka.w * v); o3 = fmaf(S[4 * m + 3], qa.w, o3);
+#pragma unroll
+          for (int c = 0; c < NC; ++c) {
+            float* Sc = S[c] + 4 * m;
+            Sc[0] = fmaf(aa.x, Sc[0], ka.x * v[c]); o[c][0] = fmaf(Sc[0], qa.x, o[c][0]);
+            Sc[1] = fmaf(aa.y, Sc[1], ka.y * v[c]); o[c][1] = fmaf(Sc[1], qa.y, o[c][1]);
+            Sc[2] = fmaf(aa.z, Sc[2], ka.z * v[c]); o[c][2] = fmaf(Sc[2], qa.z, o[c][2]);
+            Sc[3] = fmaf(aa.w, Sc[3], ka.w * v[c]); o[c][3] = fmaf(Sc[3], qa.w, o[c][3]);
+          }
         }
       }
-      float o = (o0 + o1) + (o2 + o3);
-      for (int w = 1; w < P; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
-      if (part == 0) os[tt * cols + jj] = o;
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        float oc = (o[c][0] + o[c][1]) + (o[c][2] + o[c][3]);
+        for (int w = 1; w < P; w <<= 1) oc += __shfl_xor_sync(0xffffffffu, oc, w);
+        if (part == 0) os[tt * cols + jj + c * tcols] = oc;
+      }
     }
     __syncthreads();
     for (int e = threadIdx.x; e < gn * cols; e += kThreads) {
@@ -106,13 +120,15 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
       if (jc < Dv) a.o[static_cast<long long>(tok0 + g0 + tt) * (a.heads * Dv) + head * Dv + jc] = os[e];
     }
   }
-  if (live) {
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) {
-      const int i = i0 + r;
-      if (r < rpp && i < D) Sg[static_cast<long long>(i) * Dv + j] = S[r];
+  for (int c = 0; c < NC; ++c)
+    if (live[c]) {
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        const int i = i0 + r;
+        if (r < rpp && i < D) Sg[static_cast<long long>(i) * Dv + j[c]] = S[c][r];
+      }
     }
-  }
 }
 
 // one warp per (token, head): unit RMS over vdim, weight, SiLU gate
@@ -143,15 +159,26 @@ int gla_scan(const GlaArgs& a, cudaStream_t st) {
   while (P * kRows < a.dim) P <<= 1;
   if (P > 32) return -1;   // dim <= 1024
   const int rows_per_part = ((a.dim + P - 1) / P + 3) / 4 * 4;
-  const int cols = kThreads / P;
+  const int tcols = kThreads / P;
+  // two columns per thread when that still leaves at least two CTAs per SM's worth of work
+  int sms = 148;
+  { int dev = 0; if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  const long long ctas2 = static_cast<long long>((a.vdim + 2 * tcols - 1) / (2 * tcols)) * a.heads * a.nseq;
+  const int NC = (a.vdim >= 2 * tcols && ctas2 >= sms) ? 2 : 1;
+  const int cols = tcols * NC;
   dim3 grid((a.vdim + cols - 1) / cols, a.heads, a.nseq);
   int G = kGroup;
   auto smem_for = [&](int g) { return static_cast<size_t>(g) * (3 * P * (rows_per_part + 4) + 2 * cols) * sizeof(float); };
   while (G > 1 && smem_for(G) > 44 * 1024) G >>= 1;
   const size_t smem = smem_for(G);
   if (smem > 48 * 1024) return -1;
-  if (a.t == DT_BF16) gla_scan_kernel<bf16><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G);
-  else gla_scan_kernel<float><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G);
+  if (a.t == DT_BF16) {
+    if (NC == 2) gla_scan_kernel<bf16, 2><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G);
+    else gla_scan_kernel<bf16, 1><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G);
+  } else {
+    if (NC == 2) gla_scan_kernel<float, 2><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G);
+    else gla_scan_kernel<float, 1><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

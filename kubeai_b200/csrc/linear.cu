@@ -232,6 +232,40 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(LinearArgs a) {
   }
 }
 
+// A few rows that each name their own source row, destination row and weight matrix (the expert choices of a decode step):
+// one warp per (row, output column) streams that matrix's row once, so the step reads every chosen expert's weights at
+// streaming rate instead of walking 64-row tiles that are almost empty.
+template <typename TX, typename TW, typename TY, int VEC>
+__global__ void __launch_bounds__(256) linear_picked_rows_kernel(LinearArgs a, PickedRows p) {
+  const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
+  const int n = blockIdx.x * 8 + wrp, r = blockIdx.y;
+  if (n >= a.N) return;
+  const long long src = p.src_rows ? p.src_rows[r] : r / p.src_div;
+  const long long dst = p.dst_rows[r];
+  const TX* x = static_cast<const TX*>(a.X) + src * a.ldx;
+  const TW* w = static_cast<const TW*>(a.W) + static_cast<long long>(p.groups[r]) * a.wbs + static_cast<long long>(n) * a.ldw;
+  float acc = 0.f;
+  for (int k = lane * VEC; k < a.K; k += 32 * VEC) {
+    float wv[VEC], xv[VEC];
+    if constexpr (VEC == 8) { ld8(w + k, wv); ld8(x + k, xv); } else { wv[0] = ld1(w + k); xv[0] = ld1(x + k); }
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc = fmaf(xv[v], wv[v], acc);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) st1(static_cast<TY*>(a.Y) + dst * a.ldy + n, apply_act(acc, a.act));
+}
+
+template <typename TX, typename TW, typename TY>
+int launch_picked(const LinearArgs& a, const PickedRows& p, cudaStream_t st) {
+  const bool vec = a.K % 8 == 0 && a.ldx % 8 == 0 && a.ldw % 8 == 0 && a.wbs % 8 == 0 && reinterpret_cast<uintptr_t>(a.X) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(a.W) % 16 == 0;
+  dim3 grid((a.N + 7) / 8, p.rows);
+  if (vec) linear_picked_rows_kernel<TX, TW, TY, 8><<<grid, 256, 0, st>>>(a, p);
+  else linear_picked_rows_kernel<TX, TW, TY, 1><<<grid, 256, 0, st>>>(a, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 template <typename TX, typename TW, typename TY>
 int launch_linear(const LinearArgs& a, cudaStream_t st) {
   const bool few = a.T <= 8 && !a.x_rows && !a.tile_group;
@@ -267,6 +301,14 @@ int linear(const LinearArgs& a, cudaStream_t st) {
     case 6: return launch_linear<float, float, bf16>(a, st);
     default: return launch_linear<float, float, float>(a, st);
   }
+}
+
+
+int linear_picked_rows(const LinearArgs& a, const PickedRows& p, cudaStream_t st) {
+  if (p.rows <= 0 || a.N <= 0) return 0;
+  if (!a.X || !a.W || !a.Y || a.K <= 0 || !p.dst_rows || !p.groups || (!p.src_rows && p.src_div < 1) || a.tw != a.tx) return -1;
+  if (a.tx == DT_BF16) return a.ty == DT_BF16 ? launch_picked<bf16, bf16, bf16>(a, p, st) : launch_picked<bf16, bf16, float>(a, p, st);
+  return a.ty == DT_BF16 ? launch_picked<float, float, bf16>(a, p, st) : launch_picked<float, float, float>(a, p, st);
 }
 
 }  // namespace b200

@@ -40,6 +40,15 @@ inline LinearArgs linear_args(const void* X, DType tx, const void* W, DType tw, 
   return a;
 }
 int linear(const LinearArgs& a, cudaStream_t st);
+// `rows` rows (a handful: the expert choices of a decode step), row r reading X row src_rows[r] (or r / src_div), writing Y row
+// dst_rows[r], with weight matrix W + groups[r] * wbs; a.T, a.batch, x_rows and tile_group are not used.
+struct PickedRows {
+  int rows;
+  const int* src_rows; int src_div;
+  const int* dst_rows;
+  const int* groups;
+};
+int linear_picked_rows(const LinearArgs& a, const PickedRows& p, cudaStream_t st);
 
 // ---------------------------------------------------------------- embedding, norm, activations (norm_act.cu)
 // x[t] = embed[ids[t]] + bigram[row], row = (prev * mul_prev + id * mul_cur) mod buckets, or row `buckets` when

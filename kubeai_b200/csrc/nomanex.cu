@@ -673,6 +673,18 @@ class Nomanex : public Model {
           prof_stop("moe_down");
           KRN("moe_combine", moe_combine(edown16, DT_BF16, pair_pos, topw, fo, dt, T, s.top, W, st));
           nl += 5;
+        } else if (T * s.top <= 64) {
+          // decode-sized steps: one weight-streaming pass per chosen (token, expert) pair
+          LinearArgs up = linear_args(h, dt, w.e_up, dt, eact, dt, T * s.top, s.ff, W);
+          up.wbs = static_cast<long long>(s.ff) * W; up.act = LIN_RELU2;
+          const PickedRows pu = {T * s.top, nullptr, s.top, pair_pos, topi};
+          KRN("moe_up", linear_picked_rows(up, pu, st));
+          LinearArgs dn = linear_args(eact, dt, w.e_down, dt, edown, DT_F32, T * s.top, W, s.ff);
+          dn.wbs = static_cast<long long>(W) * s.ff;
+          const PickedRows pd = {T * s.top, pair_pos, 1, pair_pos, topi};
+          KRN("moe_down", linear_picked_rows(dn, pd, st));
+          KRN("moe_combine", moe_combine(edown, DT_F32, pair_pos, topw, fo, dt, T, s.top, W, st));
+          nl += 4;
         } else {
           LinearArgs up = linear_args(h, dt, w.e_up, dt, eact, dt, cap, s.ff, W);
           up.x_rows = sorted_rows; up.tile_group = tile_group; up.wbs = static_cast<long long>(s.ff) * W; up.act = LIN_RELU2;
