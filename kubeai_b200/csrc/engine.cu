@@ -212,6 +212,7 @@ struct StepMeta {
   int T = 0, nd = 0, np = 0, S = 0, nseq = 0;
   int off_ids = 0, off_pos = 0, off_slots = 0, off_rows = 0, off_dwork = 0, off_pwork = 0, off_btab = 0;
   int off_prev = 0, off_seqtok = 0, off_seqs = 0;   // model engines: previous token and sequence of every token, per-sequence table
+  int max_ctx = 0;     // longest context (first position + tokens) among the step's sequences
   int words = 0;
   int64_t kv_tokens = 0;
   int out_tokens = 0;  // sampled rows that produce a generated token
@@ -693,6 +694,7 @@ int Engine::forward_model(const StepMeta& m, int32_t* dbuf, float* host_logits) 
   b.ids = dbuf + m.off_ids; b.prev_ids = dbuf + m.off_prev; b.pos = dbuf + m.off_pos; b.slots = dbuf + m.off_slots;
   b.rows = dbuf + m.off_rows; b.seq_of_tok = dbuf + m.off_seqtok; b.seqs = dbuf + m.off_seqs; b.btab = dbuf + m.off_btab;
   b.max_blocks = max_blocks_per_seq;
+  b.max_ctx = m.max_ctx;
   last_S = m.S;
   if (int rc = model->forward(b, sampled, host_logits, &stats.kernel_launches)) return rc == -1 ? B200_ERR_INVALID : B200_ERR_CUDA;
   return 0;
@@ -1244,6 +1246,7 @@ int Engine::pack(InFlight* f, const std::vector<std::vector<int>>* want, StepMet
       }
       int32_t* q = h + m.off_seqs + 8 * si;
       q[0] = t0; q[1] = n; q[2] = p0; q[3] = s.state_slot < 0 ? 0 : s.state_slot; q[4] = q[5] = q[6] = q[7] = 0;
+      m.max_ctx = std::max(m.max_ctx, p0 + n);
       t0 += n;
     }
   }

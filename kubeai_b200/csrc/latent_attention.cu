@@ -14,6 +14,7 @@
 
 #include <stdlib.h>
 
+#include <algorithm>
 #include <atomic>
 #include <vector>
 
@@ -171,16 +172,19 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 
 constexpr int kMaxPairs = 4;   // 16-column pairs of the latent value width per warp: kv_rank <= 8 * 4 * 16 = 512
 
-__global__ void __launch_bounds__(256) latent_attn_mma_kernel(LatentAttnArgs a, const int* seqs, int nseq, int TQ, int HB) {
+// MB = 16-row blocks per CTA: two for steps made of prompt portions (each key tile then serves twice the rows)
+template <int MB>
+__global__ void __launch_bounds__(256) latent_attn_mma_kernel(LatentAttnArgs a, const int* seqs, int nseq, int TQ, int HB, int nsplit, float* split_ws) {
   extern __shared__ __align__(16) unsigned char smraw[];
+  constexpr int R = 16 * MB;
   const int C = a.kv_rank, E = a.kv_rank + a.rot_dim, LDE = E + 8;
-  bf16* Qs = reinterpret_cast<bf16*>(smraw);                       // [16][LDE]
-  bf16* Ks = Qs + 16 * LDE;                                        // [2][kKeys][LDE]
-  float* Ss = reinterpret_cast<float*>(Ks + 2 * kKeys * LDE);      // [16][kKeys + 4]
-  bf16* Ps = reinterpret_cast<bf16*>(Ss + 16 * (kKeys + 4));       // [16][kKeys + 8]
-  float* Ms = reinterpret_cast<float*>(Ps + 16 * (kKeys + 8));     // running max [16], sum [16], rescale [16]
-  float* Ls = Ms + 16;
-  float* As = Ls + 16;
+  bf16* Qs = reinterpret_cast<bf16*>(smraw);                       // [R][LDE]
+  bf16* Ks = Qs + R * LDE;                                         // [2][kKeys][LDE]
+  float* Ss = reinterpret_cast<float*>(Ks + 2 * kKeys * LDE);      // [R][kKeys + 4]
+  bf16* Ps = reinterpret_cast<bf16*>(Ss + R * (kKeys + 4));        // [R][kKeys + 8]
+  float* Ms = reinterpret_cast<float*>(Ps + R * (kKeys + 8));      // running max [R], sum [R], rescale [R]
+  float* Ls = Ms + R;
+  float* As = Ls + R;
   // which (sequence, token tile) is this CTA's
   int idx = blockIdx.x, seq = -1, tile = 0;
   for (int s = 0; s < nseq; ++s) {
@@ -194,7 +198,10 @@ __global__ void __launch_bounds__(256) latent_attn_mma_kernel(LatentAttnArgs a, 
   const int h0 = blockIdx.y * HB;
   const int p_first = pos0 + tq0, p_last = p_first + ntq - 1;
   const int lo = max(0, p_first - a.window + 1);
-  const int ntiles = (p_last - lo) / kKeys + 1;
+  const int all_tiles = (p_last - lo) / kKeys + 1;
+  // split form (few sequences, long windows): CTA z of nsplit walks its share of the key tiles and leaves an unnormalised partial
+  const int per = (all_tiles + nsplit - 1) / nsplit;
+  const int t_begin = min(all_tiles, static_cast<int>(blockIdx.z) * per), t_end = min(all_tiles, t_begin + per);
   const int* bt = a.block_tables + static_cast<long long>(seq) * a.max_blocks;
   const bf16* cache = static_cast<const bf16*>(a.cache);
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
@@ -210,58 +217,70 @@ __global__ void __launch_bounds__(256) latent_attn_mma_kernel(LatentAttnArgs a, 
       else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
     }
   };
-  load_tile(0, 0);
-  // latent queries of the 16 rows (row r = token tq0 + r / HB, head h0 + r % HB), rounded to bf16
-  for (int e = tid; e < 16 * E; e += 256) {
+  if (t_begin < t_end) load_tile(t_begin, t_begin & 1);
+  // latent queries of the R rows (row r = token tq0 + r / HB, head h0 + r % HB), rounded to bf16
+  for (int e = tid; e < R * E; e += 256) {
     const int r = e / E, c = e - r * E, tq = r / HB, h = h0 + r % HB;
     float v = 0.f;
     if (tq < ntq && h < a.heads) v = a.qlat[(static_cast<long long>(tok0 + tq0 + tq) * a.heads + h) * E + c];
     Qs[r * LDE + c] = __float2bfloat16_rn(v);
   }
-  if (tid < 16) { Ms[tid] = -FLT_MAX; Ls[tid] = 0.f; As[tid] = 1.f; }
-  float acc[kMaxPairs][2][4];
+  if (tid < R) { Ms[tid] = -FLT_MAX; Ls[tid] = 0.f; As[tid] = 1.f; }
+  float acc[MB][kMaxPairs][2][4];
 #pragma unroll
-  for (int i = 0; i < kMaxPairs; ++i)
+  for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
+    for (int i = 0; i < kMaxPairs; ++i)
 #pragma unroll
-      for (int k = 0; k < 4; ++k) acc[i][j][k] = 0.f;
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[mb][i][j][k] = 0.f;
   const int npairs = C / 16;
   const int g = lane >> 2, t4 = lane & 3;
-  // softmax pass: thread -> (row, 4 keys)
-  const int srow = tid >> 4, sk = (tid & 15) * 4;
-  const int s_tq = srow / HB;
-  const bool s_valid = s_tq < ntq && h0 + srow % HB < a.heads;
-  const int s_pos = p_first + s_tq;
 
-  for (int ti = 0; ti < ntiles; ++ti) {
+  for (int ti = t_begin; ti < t_end; ++ti) {
     cp_async_wait_all();
     __syncthreads();
-    if (ti + 1 < ntiles) load_tile(ti + 1, (ti + 1) & 1);
+    if (ti + 1 < t_end) load_tile(ti + 1, (ti + 1) & 1);
     const bf16* Kt = Ks + static_cast<size_t>(ti & 1) * kKeys * LDE;
-    // ---- scores of this warp's 8 keys
+    // ---- scores of this warp's 8 keys, for every row block
     {
-      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      float c[MB][4];
+#pragma unroll
+      for (int mb = 0; mb < MB; ++mb) c[mb][0] = c[mb][1] = c[mb][2] = c[mb][3] = 0.f;
       const uint32_t qa = smem_addr(Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDE + 8 * (lane >> 4));
       const uint32_t ka = smem_addr(Kt + (8 * w + (lane & 7)) * LDE + 8 * (lane >> 3));
       for (int ks = 0; ks < E; ks += 32) {
-        uint32_t bq[4], a0[4];
+        uint32_t bq[4];
         ldsm_x4(bq, ka + ks * 2);   // keys x k [ks, ks + 32): b0, b1 of two k-steps
-        ldsm_x4(a0, qa + ks * 2);
-        mma16816(c, a0, bq[0], bq[1]);
-        if (ks + 16 < E) {
-          uint32_t a1[4];
-          ldsm_x4(a1, qa + (ks + 16) * 2);
-          mma16816(c, a1, bq[2], bq[3]);
+        const bool two = ks + 16 < E;
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+          uint32_t a0[4];
+          ldsm_x4(a0, qa + (mb * 16 * LDE + ks) * 2);
+          mma16816(c[mb], a0, bq[0], bq[1]);
+          if (two) {
+            uint32_t a1[4];
+            ldsm_x4(a1, qa + (mb * 16 * LDE + ks + 16) * 2);
+            mma16816(c[mb], a1, bq[2], bq[3]);
+          }
         }
       }
-      float* sp = Ss + g * (kKeys + 4) + 8 * w + 2 * t4;
-      sp[0] = c[0]; sp[1] = c[1];
-      sp[8 * (kKeys + 4)] = c[2]; sp[8 * (kKeys + 4) + 1] = c[3];
+#pragma unroll
+      for (int mb = 0; mb < MB; ++mb) {
+        float* sp = Ss + (mb * 16 + g) * (kKeys + 4) + 8 * w + 2 * t4;
+        sp[0] = c[mb][0]; sp[1] = c[mb][1];
+        sp[8 * (kKeys + 4)] = c[mb][2]; sp[8 * (kKeys + 4) + 1] = c[mb][3];
+      }
     }
     __syncthreads();
-    // ---- online softmax
-    {
+    // ---- online softmax: thread -> (row, 4 keys)
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb) {
+      const int srow = mb * 16 + (tid >> 4), sk = (tid & 15) * 4;
+      const int s_tq = srow / HB;
+      const bool s_valid = s_tq < ntq && h0 + srow % HB < a.heads;
+      const int s_pos = p_first + s_tq;
       const int j0 = lo + ti * kKeys + sk;
       float sv[4], mx = -FLT_MAX;
 #pragma unroll
@@ -275,15 +294,12 @@ __global__ void __launch_bounds__(256) latent_attn_mma_kernel(LatentAttnArgs a, 
       for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       const float m_new = fmaxf(m_old, mx);
       float sum = 0.f;
-      __nv_bfloat162 p01, p23;
       float pv[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) { pv[i] = sv[i] == -FLT_MAX ? 0.f : expf(sv[i] - m_new); sum += pv[i]; }
       for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-      p01 = __floats2bfloat162_rn(pv[0], pv[1]);
-      p23 = __floats2bfloat162_rn(pv[2], pv[3]);
-      *reinterpret_cast<__nv_bfloat162*>(Ps + srow * (kKeys + 8) + sk) = p01;
-      *reinterpret_cast<__nv_bfloat162*>(Ps + srow * (kKeys + 8) + sk + 2) = p23;
+      *reinterpret_cast<__nv_bfloat162*>(Ps + srow * (kKeys + 8) + sk) = __floats2bfloat162_rn(pv[0], pv[1]);
+      *reinterpret_cast<__nv_bfloat162*>(Ps + srow * (kKeys + 8) + sk + 2) = __floats2bfloat162_rn(pv[2], pv[3]);
       if ((tid & 15) == 0) {
         const float al = m_old == -FLT_MAX ? 0.f : expf(m_old - m_new);
         Ms[srow] = m_new;
@@ -292,56 +308,99 @@ __global__ void __launch_bounds__(256) latent_attn_mma_kernel(LatentAttnArgs a, 
       }
     }
     __syncthreads();
-    // ---- values: this warp's column pairs
+    // ---- values: this warp's column pairs, for every row block
     {
-      const float al0 = As[g], al1 = As[g + 8];
-      uint32_t pa[4][4];
+      uint32_t pa[MB][4][4];
+      float al0[MB], al1[MB];
       const uint32_t pbase = smem_addr(Ps + ((lane & 7) + 8 * ((lane >> 3) & 1)) * (kKeys + 8) + 8 * (lane >> 4));
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks) ldsm_x4(pa[ks], pbase + ks * 32);
+      for (int mb = 0; mb < MB; ++mb) {
+        al0[mb] = As[mb * 16 + g];
+        al1[mb] = As[mb * 16 + g + 8];
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) ldsm_x4(pa[mb][ks], pbase + (mb * 16 * (kKeys + 8) + ks * 16) * 2);
+      }
 #pragma unroll
       for (int i = 0; i < kMaxPairs; ++i) {
         const int pp = w + 8 * i;
         if (pp < npairs) {
 #pragma unroll
-          for (int j = 0; j < 2; ++j) { acc[i][j][0] *= al0; acc[i][j][1] *= al0; acc[i][j][2] *= al1; acc[i][j][3] *= al1; }
+          for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) { acc[mb][i][j][0] *= al0[mb]; acc[mb][i][j][1] *= al0[mb]; acc[mb][i][j][2] *= al1[mb]; acc[mb][i][j][3] *= al1[mb]; }
           const uint32_t vb = smem_addr(Kt + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDE + 16 * pp + 8 * (lane >> 4));
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
             uint32_t bv[4];
             ldsm_x4_trans(bv, vb + ks * 16 * LDE * 2);
-            mma16816(acc[i][0], pa[ks], bv[0], bv[1]);
-            mma16816(acc[i][1], pa[ks], bv[2], bv[3]);
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb) {
+              mma16816(acc[mb][i][0], pa[mb][ks], bv[0], bv[1]);
+              mma16816(acc[mb][i][1], pa[mb][ks], bv[2], bv[3]);
+            }
           }
         }
       }
     }
   }
   __syncthreads();
-  // ---- normalise and store: rows g and g + 8
+  // ---- normalise and store: rows g and g + 8 of every row block
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int r = g + 8 * half, tq = r / HB, h = h0 + r % HB;
-    if (tq >= ntq || h >= a.heads) continue;
-    const float inv = 1.0f / Ls[r];
-    float* out = a.olat + (static_cast<long long>(tok0 + tq0 + tq) * a.heads + h) * C;
+  for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
-    for (int i = 0; i < kMaxPairs; ++i) {
-      const int pp = w + 8 * i;
-      if (pp < npairs) {
+    for (int half = 0; half < 2; ++half) {
+      const int r = mb * 16 + g + 8 * half, tq = r / HB, h = h0 + r % HB;
+      if (tq >= ntq || h >= a.heads) continue;
+      const long long orow = static_cast<long long>(tok0 + tq0 + tq) * a.heads + h;
+      float inv = 1.0f / Ls[r];
+      float* out = a.olat + orow * C;
+      if (nsplit > 1) {
+        // partial: [row][split][C + 2] = unnormalised sums, running maximum, running sum
+        out = split_ws + (orow * nsplit + blockIdx.z) * (C + 2);
+        inv = 1.0f;
+        if (w == 0 && t4 == 0) { out[C] = Ms[r]; out[C + 1] = Ls[r]; }
+      }
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          out[16 * pp + 8 * j + 2 * t4] = acc[i][j][2 * half] * inv;
-          out[16 * pp + 8 * j + 2 * t4 + 1] = acc[i][j][2 * half + 1] * inv;
+      for (int i = 0; i < kMaxPairs; ++i) {
+        const int pp = w + 8 * i;
+        if (pp < npairs) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            out[16 * pp + 8 * j + 2 * t4] = acc[mb][i][j][2 * half] * inv;
+            out[16 * pp + 8 * j + 2 * t4 + 1] = acc[mb][i][j][2 * half + 1] * inv;
+          }
         }
       }
     }
+}
+
+// one warp per (token, head): combine the splits' partials
+__global__ void latent_attn_merge_kernel(const float* ws, float* olat, int C, int nsplit, long long rows) {
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const float* p = ws + row * nsplit * (C + 2);
+  float M = -FLT_MAX;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, p[s * (C + 2) + C]);
+  float L = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float m = p[s * (C + 2) + C];
+    if (m != -FLT_MAX) L += p[s * (C + 2) + C + 1] * expf(m - M);
+  }
+  const float inv = 1.0f / L;
+  for (int c = lane; c < C; c += 32) {
+    float acc = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float m = p[s * (C + 2) + C];
+      if (m != -FLT_MAX) acc = fmaf(p[s * (C + 2) + c], expf(m - M), acc);
+    }
+    olat[row * C + c] = acc * inv;
   }
 }
 
-size_t latent_mma_smem(int E) {
-  const size_t LDE = E + 8;
-  return (16 * LDE + 2 * kKeys * LDE) * 2 + 16 * (kKeys + 4) * 4 + 16 * (kKeys + 8) * 2 + 3 * 16 * 4;
+size_t latent_mma_smem(int E, int MB) {
+  const size_t LDE = E + 8, R = 16 * MB;
+  return (R * LDE + 2 * kKeys * LDE) * 2 + R * (kKeys + 4) * 4 + R * (kKeys + 8) * 2 + 3 * R * 4;
 }
 
 }  // namespace
@@ -375,15 +434,37 @@ int latent_attention(const LatentAttnArgs& a, cudaStream_t st) {
   // bf16 caches whose widths fit the fragments run on the tensor cores (B200_NX_ATTN_MMA=0: A/B knob)
   const int E = a.kv_rank + a.rot_dim;
   const char* ev = getenv("B200_NX_ATTN_MMA");
-  if (a.t == DT_BF16 && a.seqs && E % 16 == 0 && a.kv_rank % 16 == 0 && a.kv_rank <= 8 * kMaxPairs * 16 && latent_mma_smem(E) <= 220 * 1024 &&
+  if (a.t == DT_BF16 && a.seqs && E % 16 == 0 && a.kv_rank % 16 == 0 && a.kv_rank <= 8 * kMaxPairs * 16 && latent_mma_smem(E, 1) <= 220 * 1024 &&
       !(ev && atoi(ev) == 0)) {
-    const int HB = a.heads < 16 ? a.heads : 16, TQ = 16 / HB;
-    const size_t smem = latent_mma_smem(E);
-    static std::atomic<unsigned long long> attr_done{0};
     // once per device, for the largest tile the dispatch admits: the attribute is a limit, not a per-launch size
-    if (!ensure_dynamic_smem(latent_attn_mma_kernel, 220 * 1024, &attr_done)) return -2;
-    dim3 grid((a.T + TQ - 1) / TQ + a.nseq, (a.heads + HB - 1) / HB);
-    latent_attn_mma_kernel<<<grid, 256, smem, st>>>(a, a.seqs, a.nseq, TQ, HB);
+    static std::atomic<unsigned long long> attr1{0}, attr2{0};
+    const int HB = a.heads < 16 ? a.heads : 16;
+    // two row blocks when the step is mostly prompt portions and 32 rows still hold whole tokens
+    const bool two = a.T >= 2 * a.nseq && 32 / HB >= 2 && latent_mma_smem(E, 2) <= 220 * 1024;
+    const int TQ = (two ? 32 : 16) / HB;
+    // few CTAs and long windows (decode of a handful of sequences): split every window over several CTAs and merge
+    int sms = 148;
+    { int dev = 0; if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+    const int ctas = ((a.T + TQ - 1) / TQ) * ((a.heads + HB - 1) / HB);
+    const int key_tiles = (std::min(a.window, std::max(a.max_ctx, 1)) + kKeys - 1) / kKeys;
+    int nsplit = 1;
+    const char* se = getenv("B200_NX_ATTN_SPLIT");   // A/B knob: 1 = never split
+    if (a.split_ws && ctas * 2 <= sms && key_tiles >= 4) nsplit = std::min(std::min(sms / ctas, key_tiles / 2), 16);
+    if (se) nsplit = std::max(1, std::min(atoi(se), 16));
+    if (nsplit > 1 && (!a.split_ws || static_cast<long long>(a.T) * a.heads * nsplit * (a.kv_rank + 2) > a.split_ws_floats)) nsplit = 1;
+    dim3 grid((a.T + TQ - 1) / TQ + a.nseq, (a.heads + HB - 1) / HB, nsplit);
+    if (two) {
+      if (!ensure_dynamic_smem(latent_attn_mma_kernel<2>, 220 * 1024, &attr2)) return -2;
+      latent_attn_mma_kernel<2><<<grid, 256, latent_mma_smem(E, 2), st>>>(a, a.seqs, a.nseq, TQ, HB, nsplit, a.split_ws);
+    } else {
+      if (!ensure_dynamic_smem(latent_attn_mma_kernel<1>, 220 * 1024, &attr1)) return -2;
+      latent_attn_mma_kernel<1><<<grid, 256, latent_mma_smem(E, 1), st>>>(a, a.seqs, a.nseq, TQ, HB, nsplit, a.split_ws);
+    }
+    if (cudaGetLastError() != cudaSuccess) return -2;
+    if (nsplit > 1) {
+      const long long rows = static_cast<long long>(a.T) * a.heads;
+      latent_attn_merge_kernel<<<static_cast<unsigned>((rows + 3) / 4), 128, 0, st>>>(a.split_ws, a.olat, a.kv_rank, nsplit, rows);
+    }
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
   }
   const size_t smem = static_cast<size_t>(a.kv_rank + a.rot_dim + a.window) * sizeof(float);

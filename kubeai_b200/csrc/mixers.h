@@ -111,6 +111,8 @@ struct LatentAttnArgs {
   float* olat;
   int T, heads, kv_rank, rot_dim, window; float scale;
   const int* seqs; int nseq;   // the step's per-sequence table ({first row, rows, first position, ...}); needed by the tensor-core kernel
+  int max_ctx;                 // longest context (position of a last token + 1) in the step, for the split decision
+  float* split_ws; long long split_ws_floats;   // optional workspace of the split form: [rows][splits][kv_rank + 2] fp32
 };
 int latent_attention(const LatentAttnArgs& a, cudaStream_t st);
 

@@ -31,6 +31,7 @@ struct StepBatch {
   const int* seqs = nullptr;        // [nseq][8] = {first row, rows, first position, state slot, 0, 0, 0, 0}
   const int* btab = nullptr;        // [nseq][max_blocks]
   int max_blocks = 0;
+  int max_ctx = 0;                  // longest context in the step: max over sequences of first position + rows
 };
 
 struct ModelEnv {

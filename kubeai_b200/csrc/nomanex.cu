@@ -107,6 +107,8 @@ class Nomanex : public Model {
         *logits = nullptr;
   int *topi = nullptr, *sorted_rows = nullptr, *tile_group = nullptr, *pair_pos = nullptr;
   int row_cap = 0, moe_cap = 0;
+  float* split_ws = nullptr;       // partials of the split attention form (decode of a few long sequences)
+  long long split_ws_floats = 0;
   void *hsorted = nullptr, *edown16 = nullptr;   // per-expert tensor-core path: gathered inputs, bf16 expert outputs
   int *expert_rows = nullptr, *expert_rows_host = nullptr;
   std::vector<void*> allocs;
@@ -342,6 +344,10 @@ class Nomanex : public Model {
       rc |= dalloc(&scores, T * max_e * sizeof(float)) | dalloc(&topw, T * max_top * sizeof(float)) | dalloc(&topi, T * max_top * sizeof(int)) |
             dalloc(&sorted_rows, static_cast<size_t>(moe_cap) * sizeof(int)) | dalloc(&tile_group, static_cast<size_t>(moe_cap / 64) * sizeof(int)) |
             dalloc(&pair_pos, T * max_top * sizeof(int)) | mat(&eact, moe_cap, max_eff) | dalloc(&edown, static_cast<size_t>(moe_cap) * W * sizeof(float));
+    }
+    if (max_ol > 1 && dt == DT_BF16) {
+      split_ws_floats = 1024ll * (max_ol + 2 * 64);   // rows x splits <= 1024 of [kv_rank + 2] per head
+      rc |= dalloc(&split_ws, static_cast<size_t>(split_ws_floats) * sizeof(float));
     }
     if (rc) return rc;
     register_tensors();
@@ -618,7 +624,7 @@ class Nomanex : public Model {
         a.qlat = qlat; a.cache = r.cache; a.t = dt; a.positions = b.pos; a.seq_of_tok = b.seq_of_tok; a.block_tables = b.btab;
         a.max_blocks = b.max_blocks; a.page = env.page; a.olat = olat;
         a.T = T; a.heads = s.heads; a.kv_rank = C; a.rot_dim = R; a.window = std::min(s.window, env.max_model_len); a.scale = s.scale;
-        a.seqs = b.seqs; a.nseq = b.nseq;
+        a.seqs = b.seqs; a.nseq = b.nseq; a.max_ctx = b.max_ctx; a.split_ws = split_ws; a.split_ws_floats = split_ws_floats;
         KRN("latent_attention", latent_attention(a, st));
         // values: per head [T, kv_rank] x [vdim, kv_rank]^T into the head's columns of the output projection's input
         LinearArgs lv = linear_args(olat, DT_F32, w.uv, dt, ycat, dt, T, s.vdim, C);
