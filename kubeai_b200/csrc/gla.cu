@@ -16,8 +16,8 @@ namespace b200 {
 namespace {
 
 typedef __nv_bfloat16 bf16;
-__device__ __forceinline__ float ldf(const float* p) { return *p; }
-__device__ __forceinline__ float ldf(const bf16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ float ldf(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float ldf(const bf16* p) { return __bfloat162float(__ldg(p)); }
 __device__ __forceinline__ void stf(float* p, float v) { *p = v; }
 __device__ __forceinline__ void stf(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
@@ -62,24 +62,45 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
   for (int g0 = 0; g0 < n; g0 += G) {
     const int gn = min(G, n - g0);
     __syncthreads();
-    for (int e = threadIdx.x; e < gn * slice_elems; e += kThreads) {
-      const int tt = e / slice_elems, x = e - tt * slice_elems, pp = x / rpp, r = x - pp * rpp, i = pp * rpp + r;
-      float qv = 0.f, kv = 0.f, av = 0.f;
-      if (i < D) {
-        const long long row = static_cast<long long>(tok0 + g0 + tt);
-        const T* rp = base + row * a.ld;
-        const int c = head * D + i;
-        const float z = a.z[row * (a.heads * D) + c] + a.z_bias[c];
-        // log sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
-        const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
-        qv = ldf(rp + a.q_off + c) * a.q_scale;
-        kv = ldf(rp + a.k_off + c);
-        av = expf(ls * a.inv_tau);
+    // four elements per thread and round: their global loads are issued together, then converted and stored
+    for (int e0 = threadIdx.x; e0 < gn * slice_elems; e0 += 4 * kThreads) {
+      float zr[4], qr[4], kr[4];
+      int so[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int e = e0 + u * kThreads;
+        so[u] = -1;
+        zr[u] = qr[u] = kr[u] = 0.f;
+        if (e < gn * slice_elems) {
+          const int tt = e / slice_elems, x = e - tt * slice_elems, pp = x / rpp, r = x - pp * rpp, i = pp * rpp + r;
+          so[u] = (tt * 3) * Dp + pp * ps + r;
+          if (i < D) {
+            const long long row = static_cast<long long>(tok0 + g0 + tt);
+            const T* rp = base + row * a.ld;
+            const int c = head * D + i;
+            zr[u] = __ldg(a.z + row * (a.heads * D) + c) + __ldg(a.z_bias + c);
+            qr[u] = ldf(rp + a.q_off + c);
+            kr[u] = ldf(rp + a.k_off + c);
+          } else {
+            so[u] = -2 - so[u];   // a padding row: zeros
+          }
+        }
       }
-      float* s3 = sm + (tt * 3) * Dp + pp * ps + r;
-      s3[0] = qv;
-      s3[Dp] = kv;
-      s3[2 * Dp] = av;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (so[u] == -1) continue;
+        if (so[u] < -1) {
+          float* s3 = sm + (-2 - so[u]);
+          s3[0] = 0.f; s3[Dp] = 0.f; s3[2 * Dp] = 0.f;
+          continue;
+        }
+        // log sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
+        const float ls = fminf(zr[u], 0.f) - log1pf(expf(-fabsf(zr[u])));
+        float* s3 = sm + so[u];
+        s3[0] = qr[u] * a.q_scale;
+        s3[Dp] = kr[u];
+        s3[2 * Dp] = expf(ls * a.inv_tau);
+      }
     }
     for (int e = threadIdx.x; e < gn * cols; e += kThreads) {
       const int tt = e / cols, c = e - tt * cols, jc = blockIdx.x * cols + c;

@@ -245,9 +245,12 @@ __global__ void __launch_bounds__(256) latent_attn_mma_kernel(LatentAttnArgs a, 
     const bf16* Kt = Ks + static_cast<size_t>(ti & 1) * kKeys * LDE;
     // ---- scores of this warp's 8 keys, for every row block
     {
-      float c[MB][4];
+      // two accumulators per row block (even / odd k-steps): the dependent mma chain is half as long
+      float c[MB][4], c2[MB][4];
 #pragma unroll
-      for (int mb = 0; mb < MB; ++mb) c[mb][0] = c[mb][1] = c[mb][2] = c[mb][3] = 0.f;
+      for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) c[mb][i] = c2[mb][i] = 0.f;
       const uint32_t qa = smem_addr(Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDE + 8 * (lane >> 4));
       const uint32_t ka = smem_addr(Kt + (8 * w + (lane & 7)) * LDE + 8 * (lane >> 3));
       for (int ks = 0; ks < E; ks += 32) {
@@ -262,10 +265,14 @@ __global__ void __launch_bounds__(256) latent_attn_mma_kernel(LatentAttnArgs a, 
           if (two) {
             uint32_t a1[4];
             ldsm_x4(a1, qa + (mb * 16 * LDE + ks + 16) * 2);
-            mma16816(c[mb], a1, bq[2], bq[3]);
+            mma16816(c2[mb], a1, bq[2], bq[3]);
           }
         }
       }
+#pragma unroll
+      for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) c[mb][i] += c2[mb][i];
 #pragma unroll
       for (int mb = 0; mb < MB; ++mb) {
         float* sp = Ss + (mb * 16 + g) * (kKeys + 4) + 8 * w + 2 * t4;
