@@ -144,6 +144,24 @@ def test_bfloat16_per_expert_tensor_core_path_equals_the_grouped_kernel(tmp_path
     assert np.median(rel_err(per_expert, grouped)) < 0.03
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_medium_odd_shapes_on_every_projection_path(tmp_path, dtype):
+    """Sizes between the toy ones and a real layer, none of them round: projections wide enough for several tensor-core
+    weight slabs, a latent width that fits the mma fragments (80) beside one that does not (72 + 4), experts whose hidden
+    size is no multiple of 8 beside ones that are, steps above and below the per-expert threshold."""
+    layers = [(latent(heads=5, dim=24, rot_dim=16, vdim=40, kv_rank=64, window=50), dense(ff=328, limit=3.0)),
+              (gla(heads=3, dim=40, vdim=24, tau=12.0), moe(experts=10, top=3, count=5, keep=3, ff=72)),
+              (latent(heads=6, dim=16, rot_dim=4, vdim=24, kv_rank=72, window=200), moe(experts=6, top=2, count=2, keep=1, ff=20)),
+              ("weights_of", 1), (gla(heads=7, dim=8, vdim=16, tau=4.0), None)]
+    cfg, W, d = build(tmp_path, layers, seed=41, a_rank=12, width=200, vocab=301, buckets=997, mul_prev=131, mul_cur=31)
+    t = toks(300, cfg["vocab"], 42)
+    want = oracle_for(cfg, W).forward(t)
+    close = close16 if dtype == "bfloat16" else close32
+    with open_engine(d, dtype=dtype) as e:
+        close(feed_whole(e, t), want)
+        close(feed_portions(e, t, [130, 3, 150, 1]), want)
+
+
 # ---------------------------------------------------------------- prefill, decoding, portions
 def test_prefill_equals_token_by_token_decoding(mix):
     cfg, W, d, o = mix
