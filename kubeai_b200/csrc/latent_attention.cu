@@ -207,23 +207,30 @@ __global__ void __launch_bounds__(256) latent_attn_mma_kernel(LatentAttnArgs a, 
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int chunks = E / 8;   // 16-byte pieces of one cache row
 
+  // four threads per key row: one block-table lookup per thread and tile, then its 16-byte pieces at a fixed stride
   auto load_tile = [&](int ti, int buf) {
-    bf16* dst = Ks + static_cast<size_t>(buf) * kKeys * LDE;
-    const int j0 = lo + ti * kKeys;
-    for (int e = tid; e < kKeys * chunks; e += 256) {
-      const int jt = e / chunks, c = e - jt * chunks, j = j0 + jt;
-      bf16* d = dst + jt * LDE + c * 8;
-      if (j <= p_last) cp_async16(smem_addr(d), cache + (static_cast<long long>(bt[j / a.page]) * a.page + j % a.page) * E + c * 8);
-      else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+    const int jt = tid >> 2, sub = tid & 3;
+    const int j = lo + ti * kKeys + jt;
+    bf16* d = Ks + (static_cast<size_t>(buf) * kKeys + jt) * LDE;
+    if (j <= p_last) {
+      const bf16* src = cache + (static_cast<long long>(bt[j / a.page]) * a.page + j % a.page) * E;
+      for (int c = sub; c < chunks; c += 4) cp_async16(smem_addr(d + c * 8), src + c * 8);
+    } else {
+      for (int c = sub; c < chunks; c += 4) *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0, 0, 0, 0);
     }
   };
   if (t_begin < t_end) load_tile(t_begin, t_begin & 1);
   // latent queries of the R rows (row r = token tq0 + r / HB, head h0 + r % HB), rounded to bf16
-  for (int e = tid; e < R * E; e += 256) {
-    const int r = e / E, c = e - r * E, tq = r / HB, h = h0 + r % HB;
-    float v = 0.f;
-    if (tq < ntq && h < a.heads) v = a.qlat[(static_cast<long long>(tok0 + tq0 + tq) * a.heads + h) * E + c];
-    Qs[r * LDE + c] = __float2bfloat16_rn(v);
+  {
+    const int e4 = E / 4;   // float4 pieces per row (E is a multiple of 16)
+#pragma unroll 4
+    for (int e = tid; e < R * e4; e += 256) {
+      const int r = e / e4, c = (e - r * e4) * 4, tq = r / HB, h = h0 + r % HB;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (tq < ntq && h < a.heads) v = __ldg(reinterpret_cast<const float4*>(a.qlat + (static_cast<long long>(tok0 + tq0 + tq) * a.heads + h) * E + c));
+      *reinterpret_cast<__nv_bfloat162*>(Qs + r * LDE + c) = __floats2bfloat162_rn(v.x, v.y);
+      *reinterpret_cast<__nv_bfloat162*>(Qs + r * LDE + c + 2) = __floats2bfloat162_rn(v.z, v.w);
+    }
   }
   if (tid < R) { Ms[tid] = -FLT_MAX; Ls[tid] = 0.f; As[tid] = 1.f; }
   float acc[MB][kMaxPairs][2][4];
@@ -373,8 +380,7 @@ __global__ void __launch_bounds__(256) latent_attn_mma_kernel(LatentAttnArgs a, 
         if (pp < npairs) {
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
-            out[16 * pp + 8 * j + 2 * t4] = acc[mb][i][j][2 * half] * inv;
-            out[16 * pp + 8 * j + 2 * t4 + 1] = acc[mb][i][j][2 * half + 1] * inv;
+            *reinterpret_cast<float2*>(out + 16 * pp + 8 * j + 2 * t4) = make_float2(acc[mb][i][j][2 * half] * inv, acc[mb][i][j][2 * half + 1] * inv);
           }
         }
       }
