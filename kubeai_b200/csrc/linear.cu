@@ -118,7 +118,9 @@ __device__ __forceinline__ void mma_16816(float* c, const uint32_t* a, uint32_t 
 __device__ __forceinline__ bf16 to_bf16(float v) { return __float2bfloat16_rn(v); }
 __device__ __forceinline__ bf16 to_bf16(bf16 v) { return v; }
 
-template <typename TX, typename TY>
+// VEC: every row start and K are multiples of 8 elements and 16-byte aligned, so a thread stages one 8-element piece of X
+// and one of W per k-tile with 16-byte loads (thread -> row tid / 4, columns 8 (tid % 4) ...).
+template <typename TX, typename TY, bool VEC>
 __global__ void __launch_bounds__(256) linear_tile_mma_kernel(LinearArgs a) {
   constexpr int LD = BK + 8;   // 80-byte rows: the 8 rows of a fragment fall into distinct banks
   __shared__ __align__(16) bf16 Xs[BM][LD];
@@ -152,14 +154,42 @@ __global__ void __launch_bounds__(256) linear_tile_mma_kernel(LinearArgs a) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
   const bf16 zero = __float2bfloat16_rn(0.f);
+  // vector staging: this thread's row and column piece
+  const int vr = tid >> 2, vc = (tid & 3) * 8;
+  long long vx = -1, vw = -1;
+  if (VEC) {
+    int t = row0 + vr;
+    if (t >= a.T) t = -1;
+    else if (a.x_rows) t = a.x_rows[t];
+    vx = t < 0 ? -1 : static_cast<long long>(t) * a.ldx;
+    vw = col0 + vr < a.N ? static_cast<long long>(col0 + vr) * a.ldw : -1;
+  }
   for (int k0 = 0; k0 < a.K; k0 += BK) {
-    const int k = k0 + lane;
-    const bool kin = k < a.K;
+    if (VEC) {
+      const bool kin = k0 + vc < a.K;   // K is a multiple of 8: a piece is inside or outside as a whole
+      uint4 xv = make_uint4(0, 0, 0, 0), wv = make_uint4(0, 0, 0, 0);
+      if (kin && vw >= 0) wv = *reinterpret_cast<const uint4*>(W + vw + k0 + vc);
+      if (kin && vx >= 0) {
+        if constexpr (sizeof(TX) == 2) {
+          xv = *reinterpret_cast<const uint4*>(X + vx + k0 + vc);
+        } else {
+          const float4 f0 = *reinterpret_cast<const float4*>(X + vx + k0 + vc), f1 = *reinterpret_cast<const float4*>(X + vx + k0 + vc + 4);
+          __nv_bfloat162 p0 = __floats2bfloat162_rn(f0.x, f0.y), p1 = __floats2bfloat162_rn(f0.z, f0.w);
+          __nv_bfloat162 p2 = __floats2bfloat162_rn(f1.x, f1.y), p3 = __floats2bfloat162_rn(f1.z, f1.w);
+          xv = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1), *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+        }
+      }
+      *reinterpret_cast<uint4*>(&Xs[vr][vc]) = xv;
+      *reinterpret_cast<uint4*>(&Ws[vr][vc]) = wv;
+    } else {
+      const int k = k0 + lane;
+      const bool kin = k < a.K;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int r = wrp + 8 * i;
-      Xs[r][lane] = (kin && xoff[i] >= 0) ? to_bf16(X[xoff[i] + k]) : zero;
-      Ws[r][lane] = (kin && woff[i] >= 0) ? W[woff[i] + k] : zero;
+      for (int i = 0; i < 8; ++i) {
+        const int r = wrp + 8 * i;
+        Xs[r][lane] = (kin && xoff[i] >= 0) ? to_bf16(X[xoff[i] + k]) : zero;
+        Ws[r][lane] = (kin && woff[i] >= 0) ? W[woff[i] + k] : zero;
+      }
     }
     __syncthreads();
 #pragma unroll
@@ -278,8 +308,14 @@ int launch_linear(const LinearArgs& a, cudaStream_t st) {
     else linear_rows_kernel<TX, TW, TY, 1><<<grid, 256, 0, st>>>(a);
   } else {
     dim3 grid((a.N + BN - 1) / BN, (a.T + BM - 1) / BM, a.batch);
-    if constexpr (sizeof(TW) == 2) linear_tile_mma_kernel<TX, TY><<<grid, 256, 0, st>>>(a);
-    else linear_tile_kernel<TX, TW, TY><<<grid, 256, 0, st>>>(a);
+    if constexpr (sizeof(TW) == 2) {
+      const bool vec = a.K % 8 == 0 && a.ldx % 8 == 0 && a.ldw % 8 == 0 && a.xbs % 8 == 0 && a.wbs % 8 == 0 &&
+                       reinterpret_cast<uintptr_t>(a.X) % 16 == 0 && reinterpret_cast<uintptr_t>(a.W) % 16 == 0;
+      if (vec) linear_tile_mma_kernel<TX, TY, true><<<grid, 256, 0, st>>>(a);
+      else linear_tile_mma_kernel<TX, TY, false><<<grid, 256, 0, st>>>(a);
+    } else {
+      linear_tile_kernel<TX, TW, TY><<<grid, 256, 0, st>>>(a);
+    }
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
