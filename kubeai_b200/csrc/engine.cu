@@ -1998,6 +1998,7 @@ int b200_engine_forward_logits(b200_engine* e, const int32_t* ids, int32_t n, vo
   if (!e || !ids || n <= 0 || !host_logits_bf16) { set_error("bad arguments"); return B200_ERR_INVALID; }
   Engine& g = e->impl;
   if (!g.cfg.manual_step) { set_error("forward_logits needs manual_step"); return B200_ERR_INVALID; }
+  if (g.model) { set_error("forward_logits serves the built-in model; use b200_feed_step (fp32 logits of any position) on this engine"); return B200_ERR_INVALID; }
   if (n > g.Tcap || n > g.cfg.max_model_len) { set_error("too many tokens"); return B200_ERR_INVALID; }
   cudaSetDevice(g.cfg.device);
   Seq s;

@@ -10,6 +10,10 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <stdlib.h>
+
+#include <algorithm>
+
 #include "mixers.h"
 
 namespace b200 {
@@ -185,10 +189,12 @@ int gla_scan(const GlaArgs& a, cudaStream_t st) {
   int sms = 148;
   { int dev = 0; if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
   const long long ctas2 = static_cast<long long>((a.vdim + 2 * tcols - 1) / (2 * tcols)) * a.heads * a.nseq;
-  const int NC = (a.vdim >= 2 * tcols && ctas2 >= sms) ? 2 : 1;
+  int NC = (a.vdim >= 2 * tcols && ctas2 >= sms) ? 2 : 1;
+  if (const char* e = getenv("B200_GLA_NC")) NC = atoi(e) == 2 && a.vdim >= 2 * tcols ? 2 : 1;   // A/B knob
   const int cols = tcols * NC;
   dim3 grid((a.vdim + cols - 1) / cols, a.heads, a.nseq);
   int G = kGroup;
+  if (const char* e = getenv("B200_GLA_GROUP")) G = std::max(1, atoi(e));   // A/B knob: tokens staged per round
   auto smem_for = [&](int g) { return static_cast<size_t>(g) * (3 * P * (rows_per_part + 4) + 2 * cols) * sizeof(float); };
   while (G > 1 && smem_for(G) > 44 * 1024) G >>= 1;
   const size_t smem = smem_for(G);
