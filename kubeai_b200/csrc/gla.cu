@@ -3,10 +3,13 @@
 //
 // The scan is sequential in the token and exact: the same fp32 operations in the same order whether a sequence's tokens
 // arrive in one step or one at a time, so chunked prefill and decode agree bit for bit.  Parallelism comes from the
-// independent columns of S: a thread owns one value column j and a slice of the key rows, keeps that slice of the state in
-// registers for the whole step, and P = 1, 2, 4 ... row slices are reduced with shuffles.  q, k and the decay of a group
-// of tokens are staged in shared memory once per CTA; the decay is alpha = exp(inv_tau * logsigmoid(z + bias)) in fp32.
-// The state lives in HBM between steps ([slot][head][dim][vdim] fp32) and is read and written once per step.
+// independent columns of S: a thread owns one or two value columns j and a slice of the key rows, and keeps that slice of
+// the state in registers for the whole step.  The P = 1, 2, 4 ... row slices of a column live in different warps (a warp
+// reads one slice of q, k and the decay as a shared-memory broadcast); their partial outputs meet in shared memory and are
+// added in a fixed order.  The decay alpha = exp(inv_tau * logsigmoid(z + bias)) is computed once per step by its own
+// elementwise kernel, in fp32 with the accurate library functions; q, k and alpha of a group of tokens are staged in
+// shared memory once per CTA.  The state lives in HBM between steps ([slot][head][dim][vdim] fp32) and is read and
+// written once per step.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -34,24 +37,36 @@ constexpr int kThreads = 128;
 // (rows past dim are zeros; the 4-float pad puts the P slices a thread group reads at once into different banks, and a
 // thread reads its slice as float4), then v and o for the CTA's columns [G][cols] each, so the sequential token loop
 // touches shared memory only.
+// The decay of every (token, head, key channel), once per step and in place over the pre-activation:
+// alpha = exp(inv_tau * logsigmoid(z + bias)), log sigmoid(z) = min(z, 0) - log1p(exp(-|z|)), accurate fp32 functions.
+__global__ void gla_decay_kernel(float* z, const float* bias, int HD, float inv_tau, long long total) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const float v = z[i] + bias[i % HD];
+  const float ls = fminf(v, 0.f) - log1pf(expf(-fabsf(v)));
+  z[i] = expf(ls * inv_tau);
+}
+
 // NC = value columns per thread (2 when the value width keeps every SM busy with half as many CTAs: each q, k, alpha read
-// from shared memory then feeds twice the arithmetic).
+// from shared memory then feeds twice the arithmetic).  Threads of a warp share one row slice (part = thread / tcols), so a
+// shared-memory read of q, k or alpha is one broadcast; the P partial outputs of a column meet in shared memory and are
+// summed by the pass that writes the round's outputs.
 template <typename T, int NC>
 __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, int rpp, int G) {
   extern __shared__ __align__(16) float sm[];
   const int seq = blockIdx.z, head = blockIdx.y;
   const int tok0 = a.seqs[seq * 8 + 0], n = a.seqs[seq * 8 + 1], pos0 = a.seqs[seq * 8 + 2], slot = a.seqs[seq * 8 + 3];
   const int D = a.dim, Dv = a.vdim;
-  const int part = threadIdx.x % P, jj = threadIdx.x / P;
   const int tcols = kThreads / P, cols = tcols * NC;   // columns per thread group, per CTA
+  const int part = threadIdx.x / tcols, jj = threadIdx.x % tcols;
   int j[NC];
   bool live[NC];
 #pragma unroll
   for (int c = 0; c < NC; ++c) { j[c] = blockIdx.x * cols + jj + c * tcols; live[c] = j[c] < Dv; }
   const int i0 = part * rpp;
   const int ps = rpp + 4, Dp = P * ps;     // padded slice and row length
-  float* vs = sm + static_cast<size_t>(G) * 3 * Dp;
-  float* os = vs + G * cols;
+  float* vs = sm + static_cast<size_t>(G) * 3 * Dp;   // [G][cols]
+  float* os = vs + G * cols;                          // [G][P][cols]
   const T* base = static_cast<const T*>(a.qkv);
   float* Sg = a.states + ((static_cast<long long>(slot) * a.heads + head) * D) * Dv;
   float S[NC][kRows];
@@ -66,44 +81,22 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
   for (int g0 = 0; g0 < n; g0 += G) {
     const int gn = min(G, n - g0);
     __syncthreads();
-    // four elements per thread and round: their global loads are issued together, then converted and stored
-    for (int e0 = threadIdx.x; e0 < gn * slice_elems; e0 += 4 * kThreads) {
-      float zr[4], qr[4], kr[4];
-      int so[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int e = e0 + u * kThreads;
-        so[u] = -1;
-        zr[u] = qr[u] = kr[u] = 0.f;
-        if (e < gn * slice_elems) {
-          const int tt = e / slice_elems, x = e - tt * slice_elems, pp = x / rpp, r = x - pp * rpp, i = pp * rpp + r;
-          so[u] = (tt * 3) * Dp + pp * ps + r;
-          if (i < D) {
-            const long long row = static_cast<long long>(tok0 + g0 + tt);
-            const T* rp = base + row * a.ld;
-            const int c = head * D + i;
-            zr[u] = __ldg(a.z + row * (a.heads * D) + c) + __ldg(a.z_bias + c);
-            qr[u] = ldf(rp + a.q_off + c);
-            kr[u] = ldf(rp + a.k_off + c);
-          } else {
-            so[u] = -2 - so[u];   // a padding row: zeros
-          }
+    // stage q (scaled), k, alpha of the round's tokens: element x of a token's padded row belongs to slice x / rpp
+    for (int x = threadIdx.x; x < slice_elems; x += kThreads) {
+      const int pp = x / rpp, r = x - pp * rpp, i = pp * rpp + r;
+      float* s3 = sm + pp * ps + r;
+      const int c = head * D + i;
+      if (i < D) {
+#pragma unroll 4
+        for (int tt = 0; tt < gn; ++tt) {
+          const long long row = static_cast<long long>(tok0 + g0 + tt);
+          const T* rp = base + row * a.ld;
+          s3[(tt * 3) * Dp] = ldf(rp + a.q_off + c) * a.q_scale;
+          s3[(tt * 3 + 1) * Dp] = ldf(rp + a.k_off + c);
+          s3[(tt * 3 + 2) * Dp] = __ldg(a.z + row * (a.heads * D) + c);
         }
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (so[u] == -1) continue;
-        if (so[u] < -1) {
-          float* s3 = sm + (-2 - so[u]);
-          s3[0] = 0.f; s3[Dp] = 0.f; s3[2 * Dp] = 0.f;
-          continue;
-        }
-        // log sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
-        const float ls = fminf(zr[u], 0.f) - log1pf(expf(-fabsf(zr[u])));
-        float* s3 = sm + so[u];
-        s3[0] = qr[u] * a.q_scale;
-        s3[Dp] = kr[u];
-        s3[2 * Dp] = expf(ls * a.inv_tau);
+      } else {
+        for (int tt = 0; tt < gn; ++tt) { s3[(tt * 3) * Dp] = 0.f; s3[(tt * 3 + 1) * Dp] = 0.f; s3[(tt * 3 + 2) * Dp] = 0.f; }
       }
     }
     for (int e = threadIdx.x; e < gn * cols; e += kThreads) {
@@ -133,16 +126,14 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
         }
       }
 #pragma unroll
-      for (int c = 0; c < NC; ++c) {
-        float oc = (o[c][0] + o[c][1]) + (o[c][2] + o[c][3]);
-        for (int w = 1; w < P; w <<= 1) oc += __shfl_xor_sync(0xffffffffu, oc, w);
-        if (part == 0) os[tt * cols + jj + c * tcols] = oc;
-      }
+      for (int c = 0; c < NC; ++c) os[(tt * P + part) * cols + jj + c * tcols] = (o[c][0] + o[c][1]) + (o[c][2] + o[c][3]);
     }
     __syncthreads();
     for (int e = threadIdx.x; e < gn * cols; e += kThreads) {
       const int tt = e / cols, c = e - tt * cols, jc = blockIdx.x * cols + c;
-      if (jc < Dv) a.o[static_cast<long long>(tok0 + g0 + tt) * (a.heads * Dv) + head * Dv + jc] = os[e];
+      float o = 0.f;
+      for (int pp = 0; pp < P; ++pp) o += os[(tt * P + pp) * cols + c];   // slices in a fixed order
+      if (jc < Dv) a.o[static_cast<long long>(tok0 + g0 + tt) * (a.heads * Dv) + head * Dv + jc] = o;
     }
   }
 #pragma unroll
@@ -195,10 +186,14 @@ int gla_scan(const GlaArgs& a, cudaStream_t st) {
   dim3 grid((a.vdim + cols - 1) / cols, a.heads, a.nseq);
   int G = kGroup;
   if (const char* e = getenv("B200_GLA_GROUP")) G = std::max(1, atoi(e));   // A/B knob: tokens staged per round
-  auto smem_for = [&](int g) { return static_cast<size_t>(g) * (3 * P * (rows_per_part + 4) + 2 * cols) * sizeof(float); };
+  auto smem_for = [&](int g) { return static_cast<size_t>(g) * (3 * P * (rows_per_part + 4) + (1 + P) * cols) * sizeof(float); };
   while (G > 1 && smem_for(G) > 44 * 1024) G >>= 1;
   const size_t smem = smem_for(G);
   if (smem > 48 * 1024) return -1;
+  {
+    const long long total = static_cast<long long>(a.T) * a.heads * a.dim;
+    if (total > 0) gla_decay_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(a.z, a.z_bias, a.heads * a.dim, a.inv_tau, total);
+  }
   if (a.t == DT_BF16) {
     if (NC == 2) gla_scan_kernel<bf16, 2><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G);
     else gla_scan_kernel<bf16, 1><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G);

@@ -72,12 +72,13 @@ int argmax_f32(const float* logits, int* out, int S, int V, cudaStream_t st);
 // ---------------------------------------------------------------- gated linear attention (gla.cu)
 // Per sequence and head: S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T (q_t * q_scale), alpha = sigmoid(z + z_bias)^(inv_tau),
 // all in fp32.  q, k, v are column blocks of one row-major buffer (leading dimension ld, column offsets q_off / k_off /
-// v_off; heads x dim, heads x dim, heads x vdim).  z: fp32 [T, heads * dim].  states: fp32 [slot][heads][dim][vdim].
+// v_off; heads x dim, heads x dim, heads x vdim).  z: fp32 [T, heads * dim] pre-activations, replaced by the decays.  states: fp32 [slot][heads][dim][vdim].
 // seqs: int [nseq][8] = {first row, rows, first position, state slot, ...}; a sequence whose first position is 0 starts
 // from a zero state whatever its slot held.  o: fp32 [T, heads * vdim].
 struct GlaArgs {
   const void* qkv; DType t; int ld, q_off, k_off, v_off;
-  const float* z; const float* z_bias; float inv_tau, q_scale;
+  float* z; const float* z_bias; float inv_tau, q_scale;   // z is overwritten with the decays
+  int T;                                                      // rows of z (tokens in the step)
   float* states; const int* seqs; int nseq;
   int heads, dim, vdim;
   float* o;

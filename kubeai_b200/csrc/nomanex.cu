@@ -602,7 +602,7 @@ class Nomanex : public Model {
         KRN("gla_decay_proj", linear(la, st));
         GlaArgs g;
         g.qkv = inb; g.t = dt; g.ld = s.n_in; g.q_off = s.off_q; g.k_off = s.off_k; g.v_off = s.off_v;
-        g.z = z; g.z_bias = w.a2_b; g.inv_tau = 1.0f / s.tau; g.q_scale = 1.0f / sqrtf(static_cast<float>(s.dim));
+        g.z = z; g.T = T; g.z_bias = w.a2_b; g.inv_tau = 1.0f / s.tau; g.q_scale = 1.0f / sqrtf(static_cast<float>(s.dim));
         g.states = r.state; g.seqs = b.seqs; g.nseq = b.nseq;
         g.heads = s.heads; g.dim = s.dim; g.vdim = s.vdim; g.o = o32;
         KRN("gla_scan", gla_scan(g, st));
