@@ -179,6 +179,7 @@ struct Seq {
   std::atomic<int> n_cached{-1};  // prefix-hit tokens at first admission
   bool admitted = false;
   bool leaving = false;  // finished in the step being completed: swept out of the running list
+  int n_trimmed = 0;     // leading pages already returned to the pool (they lie before every layer's window); blocks[i] = -1 there
   int state_slot = -1;   // recurrent-state slot (models with per-sequence state), held while the sequence holds pages
   bool fed = false;      // tokens come from the caller step by step (b200_feed_*); nothing is sampled into toks
   // shared with API threads: guarded by m (one lock per request, so a step's 128 wake-ups do not convoy on one mutex)
@@ -356,6 +357,7 @@ struct Engine {
   std::vector<int> rows_;
   bool ensure_blocks(Seq& s, int upto);
   void release_blocks(Seq& s);
+  void trim_window(Seq& s);
   void preempt(std::shared_ptr<Seq> s);
   void finish(std::shared_ptr<Seq> s, int code);
   void admit_prefix(Seq& s);
@@ -1115,13 +1117,29 @@ bool Engine::ensure_blocks(Seq& s, int upto) {
 
 void Engine::release_blocks(Seq& s) {
   // tail blocks go to the front of the LRU free queue order first (vLLM frees in reverse)
-  for (auto it = s.blocks.rbegin(); it != s.blocks.rend(); ++it) pool.unref(*it);
+  for (auto it = s.blocks.rbegin(); it != s.blocks.rend(); ++it)
+    if (*it >= 0) pool.unref(*it);
   s.blocks.clear();
+  s.n_trimmed = 0;
   // the slot's contents are not cleared: a sequence that starts at position 0 ignores what its slot held
   if (s.state_slot >= 0) { free_slots.push_back(s.state_slot); s.state_slot = -1; }
   s.n_computed = 0;
   s.n_published = 0;
   s.chain_uid = 0;
+}
+
+// Sliding-window designs: a page whose last token lies before the window of the next token to be computed is never read
+// again by any layer (windows only move forward); it goes back to the pool now instead of when the sequence ends.
+void Engine::trim_window(Seq& s) {
+  const int w = model ? model->cache_window() : 0;
+  if (w <= 0) return;
+  const int first_needed = s.n_computed - w + 1;          // oldest position the next token can see
+  const int upto = std::min(first_needed / kPage, static_cast<int>(s.blocks.size()));   // pages [0, upto) end before it
+  for (int b = s.n_trimmed; b < upto; ++b) {
+    if (s.blocks[b] >= 0) pool.unref(s.blocks[b]);
+    s.blocks[b] = -1;
+  }
+  if (upto > s.n_trimmed) s.n_trimmed = upto;
 }
 
 void Engine::preempt(std::shared_ptr<Seq> s) {
@@ -1405,6 +1423,7 @@ int Engine::complete(InFlight& f, const StepMeta& m, b200_step_info* info) {
       s.chain_uid = pool.publish(s.blocks[b], s.chain_uid, &s.toks[static_cast<size_t>(b) * kPage]);
       ++s.n_published;
     }
+    trim_window(s);
     if (!samples) continue;
     const int32_t t = sampled_host[ri++];
     s.toks.push_back(t);
@@ -1538,7 +1557,7 @@ int Engine::feed_step(const b200_feed_entry* entries, int n, float* logits_out, 
     for (int i = 0; i < n; ++i) f.sched[i].s->toks.resize(f.sched[i].s->toks.size() - entries[i].n_tokens);
     return rc;
   }
-  for (int i = 0; i < n; ++i) f.sched[i].s->n_computed += f.sched[i].n;
+  for (int i = 0; i < n; ++i) { f.sched[i].s->n_computed += f.sched[i].n; trim_window(*f.sched[i].s); }
   float ms = 0.f;
   cudaEventElapsedTime(&ms, ev0, ev1);
   {

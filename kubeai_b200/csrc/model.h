@@ -58,6 +58,9 @@ class Model {
   virtual int vocab() const = 0;
   virtual size_t cache_bytes_per_block(int page) const = 0;   // over all layers that cache per token
   virtual size_t state_bytes_per_slot() const = 0;            // over all recurrent layers (0: no slots needed)
+  // the most tokens back any caching layer looks (itself included); 0 = some layer sees the whole sequence.  The engine
+  // returns pages that lie wholly before every such window to the pool while the sequence is still running.
+  virtual int cache_window() const { return 0; }
   // allocate weights (unset), activations for env.Tcap tokens, caches for env.num_blocks pages, states for env.num_slots
   virtual int init(const ModelEnv& env) = 0;
   // sizes that only the checkpoint's tensor shapes give; called before init() when there is a checkpoint

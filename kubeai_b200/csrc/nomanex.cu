@@ -137,6 +137,15 @@ class Nomanex : public Model {
       if (s.mixer == MIX_LATENT) b += static_cast<size_t>(page) * (s.kv_rank + s.rot_dim) * dtype_bytes(dt);
     return b;
   }
+  int cache_window() const override {
+    int w = 0;
+    for (auto& s : spec)
+      if (s.mixer == MIX_LATENT) {
+        if (s.window >= (1 << 30)) return 0;
+        w = std::max(w, s.window);
+      }
+    return w;
+  }
   size_t state_bytes_per_slot() const override {
     size_t b = 0;
     for (auto& s : spec)

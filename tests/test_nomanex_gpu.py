@@ -51,6 +51,15 @@ def mix(tmp_path_factory):
     return cfg, W, d, oracle_for(cfg, W)
 
 
+@pytest.fixture(scope="module")
+def mix_wide(tmp_path_factory):
+    """The same stack with one window longer than any test sequence: no page falls behind every window, so a sequence
+    holds all its pages and a small pool really fills."""
+    layers = [(latent(window=500), dense())] + MIX[1:]
+    cfg, W, d = build(tmp_path_factory.mktemp("mixw"), layers, seed=5)
+    return cfg, W, d, oracle_for(cfg, W)
+
+
 # ---------------------------------------------------------------- each mechanism alone
 @pytest.mark.parametrize("name,layers", [
     ("gla", [(gla(), None)]),
@@ -262,9 +271,37 @@ def feed_portions_on(e, r, tokens, sizes):
     return np.concatenate(outs)
 
 
-def test_a_step_over_the_pool_is_refused_and_leaves_the_engine_usable(mix):
+def test_pages_behind_every_window_go_back_to_the_pool_while_the_sequence_runs(tmp_path):
+    """Two 380-token sequences side by side in a pool that could not hold both whole (30 pages of 16 tokens for 2 x 24):
+    pages that no layer's window reaches any more are returned as the sequences advance, and the logits do not change."""
+    cfg, W, d = build(tmp_path, [(latent(window=20), dense()), (gla(), None), (latent(window=33, kv_rank=16, rot_dim=16), None)], seed=61)
+    o = oracle_for(cfg, W)
+    seqs = [toks(380, cfg["vocab"], 62 + i) for i in range(2)]
+    want = [o.forward(t) for t in seqs]
+    with open_engine(d, max_tokens=400, max_seqs=2, blocks=30, budget=64) as e:
+        rids = [e.feed_open() for _ in seqs]
+        got = [[], []]
+        at = 0
+        sizes = [16, 7, 16, 1, 2, 16]
+        i = 0
+        while at < 380:
+            n = min(sizes[i % len(sizes)], 380 - at)
+            out = e.feed_step([(r, t[at:at + n], list(range(n))) for r, t in zip(rids, seqs)])
+            got[0].append(out[:n])
+            got[1].append(out[n:])
+            at += n
+            i += 1
+            assert e.stats().kv_blocks_free >= 30 - 2 * 5       # window 33 + a 16-token portion: at most 5 pages each
+        for r in rids:
+            e.feed_close(r)
+        assert e.stats().kv_blocks_free == 30
+    for k in range(2):
+        close32(np.concatenate(got[k]), want[k], 3)
+
+
+def test_a_step_over_the_pool_is_refused_and_leaves_the_engine_usable(mix_wide):
     from kubeai_b200 import B200Error
-    cfg, W, d, o = mix
+    cfg, W, d, o = mix_wide
     t = toks(40, cfg["vocab"], 30)
     with open_engine(d, max_tokens=48, max_seqs=2, blocks=3) as e:
         a, b = e.feed_open(), e.feed_open()
@@ -403,9 +440,9 @@ def test_greedy_generation_through_submit_scheduler_and_sampler(mix, dtype):
                 assert got[0] == int(np.argmax(o.forward(p)[-1]))
 
 
-def test_preemption_recomputes_state_from_the_start(mix):
+def test_preemption_recomputes_state_from_the_start(mix_wide):
     """A pool too small for all running sequences to finish: the scheduler preempts and recomputes; outputs do not change."""
-    cfg, W, d, o = mix
+    cfg, W, d, o = mix_wide
     prompts = [toks(n, cfg["vocab"], 60 + i) for i, n in enumerate((30, 28, 31))]
     with open_engine(d, max_tokens=64, max_seqs=3, budget=64, blocks=8) as e:
         outs = e.generate(prompts, max_tokens=20)
