@@ -169,6 +169,9 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 constexpr int kMaxPairs = 4;   // 16-column pairs of the latent value width per warp: kv_rank <= 8 * 4 * 16 = 512
 
@@ -411,6 +414,236 @@ __global__ void latent_attn_merge_kernel(const float* ws, float* olat, int C, in
   }
 }
 
+// ---------------------------------------------------------------- wide form for long prompt portions
+// 64 query rows per CTA (TQ = 64 / HB tokens x HB heads) against key tiles of 32: every key row fetched from the pages
+// serves twice the rows of the 32-row form, and every value fragment read from shared memory feeds eight mma instead of
+// four.  Scores: warp w owns row block w % 4 and key half w / 4 (16 x 16 per k-step: one query and one key ldmatrix for two
+// mma).  Softmax: four threads per row, eight keys each.  Values: warp w owns the same column pairs as above, for all four
+// row blocks.  No split form: steps that take this kernel have CTAs enough.
+constexpr int kWideKeys = 32;
+constexpr int kWideRows = 64;
+
+__global__ void __launch_bounds__(256) latent_attn_mma_wide_kernel(LatentAttnArgs a, const int* seqs, int nseq, int TQ, int HB, int NST) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  constexpr int R = kWideRows, MB = R / 16, KT = kWideKeys, LDS = KT + 4, LDP = KT + 8;
+  const int C = a.kv_rank, E = a.kv_rank + a.rot_dim, LDE = E + 8;
+  bf16* Qs = reinterpret_cast<bf16*>(smraw);                  // [R][LDE]
+  bf16* Ks = Qs + R * LDE;                                    // [NST][KT][LDE], NST = 2 or 3 key tiles in flight
+  float* Ss = reinterpret_cast<float*>(Ks + NST * KT * LDE);  // [R][LDS]
+  bf16* Ps = reinterpret_cast<bf16*>(Ss + R * LDS);           // [R][LDP]
+  float* Ms = reinterpret_cast<float*>(Ps + R * LDP);         // running max [R], sum [R], rescale [R]
+  float* Ls = Ms + R;
+  float* As = Ls + R;
+  int idx = blockIdx.x, seq = -1, tile = 0;
+  for (int s = 0; s < nseq; ++s) {
+    const int tiles = (seqs[s * 8 + 1] + TQ - 1) / TQ;
+    if (idx < tiles) { seq = s; tile = idx; break; }
+    idx -= tiles;
+  }
+  if (seq < 0) return;
+  const int tok0 = seqs[seq * 8 + 0], n = seqs[seq * 8 + 1], pos0 = seqs[seq * 8 + 2];
+  const int tq0 = tile * TQ, ntq = min(TQ, n - tq0);
+  const int h0 = blockIdx.y * HB;
+  const int p_first = pos0 + tq0, p_last = p_first + ntq - 1;
+  const int lo = max(0, p_first - a.window + 1);
+  const int ntiles = (p_last - lo) / KT + 1;
+  const int* bt = a.block_tables + static_cast<long long>(seq) * a.max_blocks;
+  const bf16* cache = static_cast<const bf16*>(a.cache);
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int chunks = E / 8;   // 16-byte pieces of one cache row
+
+  // eight threads per key row: one block-table lookup per thread and tile, read one tile ahead of its use (tiles are
+  // loaded in order), so that the copies of a tile are not issued behind a dependent global load
+  int blk_next = 0;
+  {
+    const int j = lo + (tid >> 3);
+    if (j <= p_last) blk_next = bt[j / a.page];
+  }
+  auto load_tile = [&](int ti, int buf) {
+    const int jt = tid >> 3, sub = tid & 7;
+    const int j = lo + ti * KT + jt;
+    bf16* d = Ks + (static_cast<size_t>(buf) * KT + jt) * LDE;
+    const int blk = blk_next;
+    if (j + KT <= p_last) blk_next = bt[(j + KT) / a.page];
+    if (j <= p_last) {
+      const bf16* src = cache + (static_cast<long long>(blk) * a.page + j % a.page) * E;
+      for (int c = sub; c < chunks; c += 8) cp_async16(smem_addr(d + c * 8), src + c * 8);
+    } else {
+      for (int c = sub; c < chunks; c += 8) *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0, 0, 0, 0);
+    }
+  };
+  for (int t = 0; t < NST - 1; ++t) {
+    if (t < ntiles) load_tile(t, t);
+    cp_async_commit();
+  }
+  {
+    const int e4 = E / 4;
+#pragma unroll 4
+    for (int e = tid; e < R * e4; e += 256) {
+      const int r = e / e4, c = (e - r * e4) * 4, tq = r / HB, h = h0 + r % HB;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (tq < ntq && h < a.heads) v = __ldg(reinterpret_cast<const float4*>(a.qlat + (static_cast<long long>(tok0 + tq0 + tq) * a.heads + h) * E + c));
+      *reinterpret_cast<__nv_bfloat162*>(Qs + r * LDE + c) = __floats2bfloat162_rn(v.x, v.y);
+      *reinterpret_cast<__nv_bfloat162*>(Qs + r * LDE + c + 2) = __floats2bfloat162_rn(v.z, v.w);
+    }
+  }
+  if (tid < R) { Ms[tid] = -FLT_MAX; Ls[tid] = 0.f; As[tid] = 1.f; }
+  float acc[MB][kMaxPairs][2][4];
+#pragma unroll
+  for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+    for (int i = 0; i < kMaxPairs; ++i)
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[mb][i][j][k] = 0.f;
+  const int npairs = C / 16;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int smb = w & 3, skh = w >> 2;   // scores: this warp's row block and key half
+
+  int buf = 0;   // ti % NST
+  for (int ti = 0; ti < ntiles; ++ti) {
+    // one group is committed per tile (an empty one past the end), so all but the newest NST - 2 have landed
+    if (NST == 3) cp_async_wait_group<1>(); else cp_async_wait_group<0>();
+    __syncthreads();
+    {
+      const int nb = buf == 0 ? NST - 1 : buf - 1;   // the buffer read in the iteration before this one
+      if (ti + NST - 1 < ntiles) load_tile(ti + NST - 1, nb);
+      cp_async_commit();
+    }
+    const bf16* Kt = Ks + static_cast<size_t>(buf) * KT * LDE;
+    buf = buf + 1 == NST ? 0 : buf + 1;
+    // ---- scores: 16 rows x 16 keys per warp
+    {
+      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f}, d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint32_t qa = smem_addr(Qs + (smb * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDE + 8 * (lane >> 4));
+      const uint32_t ka = smem_addr(Kt + (skh * 16 + (lane & 7) + 8 * (lane >> 4)) * LDE + 8 * ((lane >> 3) & 1));
+      // E is a multiple of 16: pairs of k-steps with all four fragment loads ahead of the four mma, then an odd last one
+      int ks = 0;
+#pragma unroll 2
+      for (; ks + 32 <= E; ks += 32) {
+        uint32_t af[4], bf[4], ag[4], bg[4];
+        ldsm_x4(af, qa + ks * 2);
+        ldsm_x4(bf, ka + ks * 2);     // keys 0-7: k lo, k hi; keys 8-15: k lo, k hi
+        ldsm_x4(ag, qa + (ks + 16) * 2);
+        ldsm_x4(bg, ka + (ks + 16) * 2);
+        mma16816(c0, af, bf[0], bf[1]);
+        mma16816(c1, af, bf[2], bf[3]);
+        mma16816(d0, ag, bg[0], bg[1]);
+        mma16816(d1, ag, bg[2], bg[3]);
+      }
+      if (ks < E) {
+        uint32_t af[4], bf[4];
+        ldsm_x4(af, qa + ks * 2);
+        ldsm_x4(bf, ka + ks * 2);
+        mma16816(c0, af, bf[0], bf[1]);
+        mma16816(c1, af, bf[2], bf[3]);
+      }
+      float* sp = Ss + (smb * 16 + g) * LDS + skh * 16 + 2 * t4;
+      sp[0] = c0[0] + d0[0]; sp[1] = c0[1] + d0[1];
+      sp[8 * LDS] = c0[2] + d0[2]; sp[8 * LDS + 1] = c0[3] + d0[3];
+      sp[8] = c1[0] + d1[0]; sp[9] = c1[1] + d1[1];
+      sp[8 * LDS + 8] = c1[2] + d1[2]; sp[8 * LDS + 9] = c1[3] + d1[3];
+    }
+    __syncthreads();
+    // ---- online softmax: thread -> (row, 8 keys)
+    {
+      const int srow = tid >> 2, sk = (tid & 3) * 8;
+      const int s_tq = srow / HB;
+      const bool s_valid = s_tq < ntq && h0 + srow % HB < a.heads;
+      const int s_pos = p_first + s_tq;
+      const int j0 = lo + ti * KT + sk;
+      float sv[8], mx = -FLT_MAX;
+      const float4 x0 = *reinterpret_cast<const float4*>(Ss + srow * LDS + sk);
+      const float4 x1 = *reinterpret_cast<const float4*>(Ss + srow * LDS + sk + 4);
+      const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int j = j0 + i;
+        const bool vis = s_valid && j <= s_pos && j > s_pos - a.window;
+        sv[i] = vis ? xs[i] * a.scale : -FLT_MAX;
+        mx = fmaxf(mx, sv[i]);
+      }
+      const float m_old = Ms[srow];
+      for (int o = 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float m_new = fmaxf(m_old, mx);
+      float sum = 0.f;
+      float pv[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { pv[i] = sv[i] == -FLT_MAX ? 0.f : expf(sv[i] - m_new); sum += pv[i]; }
+      for (int o = 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+      for (int i = 0; i < 8; i += 2) *reinterpret_cast<__nv_bfloat162*>(Ps + srow * LDP + sk + i) = __floats2bfloat162_rn(pv[i], pv[i + 1]);
+      __syncwarp();
+      if ((tid & 3) == 0) {
+        const float al = m_old == -FLT_MAX ? 0.f : expf(m_old - m_new);
+        Ms[srow] = m_new;
+        Ls[srow] = Ls[srow] * al + sum;
+        As[srow] = m_new == -FLT_MAX ? 1.f : al;
+      }
+    }
+    __syncthreads();
+    // ---- values: this warp's column pairs, for every row block
+    {
+      uint32_t pa[MB][2][4];
+      float al0[MB], al1[MB];
+      const uint32_t pbase = smem_addr(Ps + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDP + 8 * (lane >> 4));
+#pragma unroll
+      for (int mb = 0; mb < MB; ++mb) {
+        al0[mb] = As[mb * 16 + g];
+        al1[mb] = As[mb * 16 + g + 8];
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) ldsm_x4(pa[mb][ks], pbase + (mb * 16 * LDP + ks * 16) * 2);
+      }
+#pragma unroll
+      for (int i = 0; i < kMaxPairs; ++i) {
+        const int pp = w + 8 * i;
+        if (pp < npairs) {
+#pragma unroll
+          for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) { acc[mb][i][j][0] *= al0[mb]; acc[mb][i][j][1] *= al0[mb]; acc[mb][i][j][2] *= al1[mb]; acc[mb][i][j][3] *= al1[mb]; }
+          const uint32_t vb = smem_addr(Kt + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDE + 16 * pp + 8 * (lane >> 4));
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) {
+            uint32_t bv[4];
+            ldsm_x4_trans(bv, vb + ks * 16 * LDE * 2);
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb) {
+              mma16816(acc[mb][i][0], pa[mb][ks], bv[0], bv[1]);
+              mma16816(acc[mb][i][1], pa[mb][ks], bv[2], bv[3]);
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = mb * 16 + g + 8 * half, tq = r / HB, h = h0 + r % HB;
+      if (tq >= ntq || h >= a.heads) continue;
+      const float inv = 1.0f / Ls[r];
+      float* out = a.olat + (static_cast<long long>(tok0 + tq0 + tq) * a.heads + h) * C;
+#pragma unroll
+      for (int i = 0; i < kMaxPairs; ++i) {
+        const int pp = w + 8 * i;
+        if (pp < npairs) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            *reinterpret_cast<float2*>(out + 16 * pp + 8 * j + 2 * t4) = make_float2(acc[mb][i][j][2 * half] * inv, acc[mb][i][j][2 * half + 1] * inv);
+        }
+      }
+    }
+}
+
+size_t latent_mma_wide_smem(int E, int stages) {
+  const size_t LDE = E + 8, R = kWideRows, KT = kWideKeys;
+  return (R * LDE + stages * KT * LDE) * 2 + R * (KT + 4) * 4 + R * (KT + 8) * 2 + 3 * R * 4;
+}
+
 size_t latent_mma_smem(int E, int MB) {
   const size_t LDE = E + 8, R = 16 * MB;
   return (R * LDE + 2 * kKeys * LDE) * 2 + R * (kKeys + 4) * 4 + R * (kKeys + 8) * 2 + 3 * R * 4;
@@ -465,6 +698,19 @@ int latent_attention(const LatentAttnArgs& a, cudaStream_t st) {
     if (a.split_ws && ctas * 2 <= sms && key_tiles >= 4) nsplit = std::min(std::min(sms / ctas, key_tiles / 2), 16);
     if (se) nsplit = std::max(1, std::min(atoi(se), 16));
     if (nsplit > 1 && (!a.split_ws || static_cast<long long>(a.T) * a.heads * nsplit * (a.kv_rank + 2) > a.split_ws_floats)) nsplit = 1;
+    // steps of long prompt portions with CTAs enough for every SM: 64 rows per CTA (B200_NX_ATTN_WIDE=1 forces, 0 forbids)
+    const int TQW = kWideRows / HB;
+    const char* we = getenv("B200_NX_ATTN_WIDE");
+    bool wide = two && a.T >= 4 * a.nseq && ((a.T + TQW - 1) / TQW) * ((a.heads + HB - 1) / HB) >= sms;
+    if (we) wide = two && atoi(we) != 0;
+    if (wide && latent_mma_wide_smem(E, 2) <= 220 * 1024 && !se) {
+      static std::atomic<unsigned long long> attrw{0};
+      if (!ensure_dynamic_smem(latent_attn_mma_wide_kernel, 220 * 1024, &attrw)) return -2;
+      const int stages = latent_mma_wide_smem(E, 3) <= 220 * 1024 ? 3 : 2;
+      dim3 gridw((a.T + TQW - 1) / TQW + a.nseq, (a.heads + HB - 1) / HB);
+      latent_attn_mma_wide_kernel<<<gridw, 256, latent_mma_wide_smem(E, stages), st>>>(a, a.seqs, a.nseq, TQW, HB, stages);
+      return cudaGetLastError() == cudaSuccess ? 0 : -2;
+    }
     dim3 grid((a.T + TQ - 1) / TQ + a.nseq, (a.heads + HB - 1) / HB, nsplit);
     if (two) {
       if (!ensure_dynamic_smem(latent_attn_mma_kernel<2>, 220 * 1024, &attr2)) return -2;

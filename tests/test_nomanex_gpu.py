@@ -127,9 +127,18 @@ def test_bfloat16_tensor_core_attention_equals_the_plain_kernel(tmp_path, monkey
     monkeypatch.setenv("B200_NX_ATTN_SPLIT", "3")      # every window cut over three CTAs and merged
     with open_engine(d, dtype="bfloat16") as e:
         split = feed_portions(e, t, [67, 2, 90, 1])
+    monkeypatch.delenv("B200_NX_ATTN_SPLIT")
+    monkeypatch.setenv("B200_NX_ATTN_WIDE", "1")       # the 64-row kernel of large prompt steps, forced on this small one
+    with open_engine(d, dtype="bfloat16") as e:
+        wide = feed_whole(e, t)
+        wide_cut = feed_portions(e, t, [67, 2, 90, 1])
     close16(whole, want)
     close16(cut, want)
     close16(split, want)
+    close16(wide, want)
+    close16(wide_cut, want)
+    assert np.median(rel_err(wide, plain)) < 0.02 and np.median(rel_err(wide_cut, plain)) < 0.02
+    assert rel_err(wide, plain).max() < 0.1 and rel_err(wide_cut, plain).max() < 0.1
     assert np.median(rel_err(whole, plain)) < 0.02 and np.median(rel_err(cut, plain)) < 0.02
     assert rel_err(whole, plain).max() < 0.1 and rel_err(cut, plain).max() < 0.1
     assert np.median(rel_err(split, cut)) < 0.02 and rel_err(split, cut).max() < 0.1
