@@ -478,7 +478,7 @@ __global__ void __launch_bounds__(256) latent_attn_mma_wide_kernel(LatentAttnArg
   }
   {
     const int e4 = E / 4;
-#pragma unroll 4
+#pragma unroll 12
     for (int e = tid; e < R * e4; e += 256) {
       const int r = e / e4, c = (e - r * e4) * 4, tq = r / HB, h = h0 + r % HB;
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -500,18 +500,18 @@ __global__ void __launch_bounds__(256) latent_attn_mma_wide_kernel(LatentAttnArg
   const int npairs = C / 16;
   const int g = lane >> 2, t4 = lane & 3;
   const int smb = w & 3, skh = w >> 2;   // scores: this warp's row block and key half
+  const float scale_log2 = a.scale * 1.4426950408889634f;
 
+  // Two barriers per tile.  One group is committed per tile (an empty one past the end), so waiting for all but the newest
+  // NST - 2 means: the next tile to be read has landed.  Tile ti + NST - 1 is fetched after the barrier behind the scores of
+  // tile ti, into the buffer that the values of tile ti - 1 read; the wait for tile ti + 1 stands before the barrier
+  // between softmax and values, which therefore also publishes that tile to every warp.
+  if (NST == 3) cp_async_wait_group<1>(); else cp_async_wait_group<0>();
+  __syncthreads();
   int buf = 0;   // ti % NST
   for (int ti = 0; ti < ntiles; ++ti) {
-    // one group is committed per tile (an empty one past the end), so all but the newest NST - 2 have landed
-    if (NST == 3) cp_async_wait_group<1>(); else cp_async_wait_group<0>();
-    __syncthreads();
-    {
-      const int nb = buf == 0 ? NST - 1 : buf - 1;   // the buffer read in the iteration before this one
-      if (ti + NST - 1 < ntiles) load_tile(ti + NST - 1, nb);
-      cp_async_commit();
-    }
     const bf16* Kt = Ks + static_cast<size_t>(buf) * KT * LDE;
+    const int nb = buf == 0 ? NST - 1 : buf - 1;
     buf = buf + 1 == NST ? 0 : buf + 1;
     // ---- scores: 16 rows x 16 keys per warp
     {
@@ -546,7 +546,9 @@ __global__ void __launch_bounds__(256) latent_attn_mma_wide_kernel(LatentAttnArg
       sp[8 * LDS + 8] = c1[2] + d1[2]; sp[8 * LDS + 9] = c1[3] + d1[3];
     }
     __syncthreads();
-    // ---- online softmax: thread -> (row, 8 keys)
+    if (ti + NST - 1 < ntiles) load_tile(ti + NST - 1, nb);
+    cp_async_commit();
+    // ---- online softmax: thread -> (row, 8 keys); scores in units of log 2 so that the exponentials are single ex2
     {
       const int srow = tid >> 2, sk = (tid & 3) * 8;
       const int s_tq = srow / HB;
@@ -561,27 +563,31 @@ __global__ void __launch_bounds__(256) latent_attn_mma_wide_kernel(LatentAttnArg
       for (int i = 0; i < 8; ++i) {
         const int j = j0 + i;
         const bool vis = s_valid && j <= s_pos && j > s_pos - a.window;
-        sv[i] = vis ? xs[i] * a.scale : -FLT_MAX;
+        sv[i] = vis ? xs[i] * scale_log2 : -FLT_MAX;
         mx = fmaxf(mx, sv[i]);
       }
       const float m_old = Ms[srow];
       for (int o = 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-      const float m_new = fmaxf(m_old, mx);
+      // the reference point of the exponentials follows the maximum only when that has grown by more than kLazyMax: terms
+      // stay below 2^kLazyMax, the final division cancels the reference point, and most tiles leave the accumulators alone
+      constexpr float kLazyMax = 8.f;
+      const float m_new = (m_old == -FLT_MAX || mx > m_old + kLazyMax) ? fmaxf(m_old, mx) : m_old;
       float sum = 0.f;
       float pv[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) { pv[i] = sv[i] == -FLT_MAX ? 0.f : expf(sv[i] - m_new); sum += pv[i]; }
+      for (int i = 0; i < 8; ++i) { pv[i] = sv[i] == -FLT_MAX ? 0.f : exp2f(sv[i] - m_new); sum += pv[i]; }
       for (int o = 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
 #pragma unroll
       for (int i = 0; i < 8; i += 2) *reinterpret_cast<__nv_bfloat162*>(Ps + srow * LDP + sk + i) = __floats2bfloat162_rn(pv[i], pv[i + 1]);
       __syncwarp();
       if ((tid & 3) == 0) {
-        const float al = m_old == -FLT_MAX ? 0.f : expf(m_old - m_new);
+        const float al = m_old == -FLT_MAX ? 0.f : exp2f(m_old - m_new);
         Ms[srow] = m_new;
         Ls[srow] = Ls[srow] * al + sum;
         As[srow] = m_new == -FLT_MAX ? 1.f : al;
       }
     }
+    if (NST == 3) cp_async_wait_group<1>(); else cp_async_wait_group<0>();
     __syncthreads();
     // ---- values: this warp's column pairs, for every row block
     {
@@ -595,14 +601,21 @@ __global__ void __launch_bounds__(256) latent_attn_mma_wide_kernel(LatentAttnArg
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks) ldsm_x4(pa[mb][ks], pbase + (mb * 16 * LDP + ks * 16) * 2);
       }
+      // after the first tiles a row's maximum seldom moves: the accumulators are rescaled only when some factor is not 1
+      bool moved = false;
+#pragma unroll
+      for (int mb = 0; mb < MB; ++mb) moved = moved || al0[mb] != 1.f || al1[mb] != 1.f;
+      moved = __any_sync(0xffffffffu, moved);
 #pragma unroll
       for (int i = 0; i < kMaxPairs; ++i) {
         const int pp = w + 8 * i;
         if (pp < npairs) {
+          if (moved) {
 #pragma unroll
-          for (int mb = 0; mb < MB; ++mb)
+            for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
-            for (int j = 0; j < 2; ++j) { acc[mb][i][j][0] *= al0[mb]; acc[mb][i][j][1] *= al0[mb]; acc[mb][i][j][2] *= al1[mb]; acc[mb][i][j][3] *= al1[mb]; }
+              for (int j = 0; j < 2; ++j) { acc[mb][i][j][0] *= al0[mb]; acc[mb][i][j][1] *= al0[mb]; acc[mb][i][j][2] *= al1[mb]; acc[mb][i][j][3] *= al1[mb]; }
+          }
           const uint32_t vb = smem_addr(Kt + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDE + 16 * pp + 8 * (lane >> 4));
 #pragma unroll
           for (int ks = 0; ks < 2; ++ks) {
