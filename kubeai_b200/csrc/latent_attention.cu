@@ -716,10 +716,11 @@ int latent_attention(const LatentAttnArgs& a, cudaStream_t st) {
     const char* we = getenv("B200_NX_ATTN_WIDE");
     bool wide = two && a.T >= 4 * a.nseq && ((a.T + TQW - 1) / TQW) * ((a.heads + HB - 1) / HB) >= sms;
     if (we) wide = two && atoi(we) != 0;
-    if (wide && latent_mma_wide_smem(E, 2) <= 220 * 1024 && !se) {
+    // three key buffers: every latent width whose 32-row form fits shared memory also fits them
+    constexpr int stages = 3;
+    if (wide && latent_mma_wide_smem(E, stages) <= 220 * 1024 && !se) {
       static std::atomic<unsigned long long> attrw{0};
       if (!ensure_dynamic_smem(latent_attn_mma_wide_kernel, 220 * 1024, &attrw)) return -2;
-      const int stages = latent_mma_wide_smem(E, 3) <= 220 * 1024 ? 3 : 2;
       dim3 gridw((a.T + TQW - 1) / TQW + a.nseq, (a.heads + HB - 1) / HB);
       latent_attn_mma_wide_kernel<<<gridw, 256, latent_mma_wide_smem(E, stages), st>>>(a, a.seqs, a.nseq, TQW, HB, stages);
       return cudaGetLastError() == cudaSuccess ? 0 : -2;
