@@ -144,6 +144,32 @@ def test_bfloat16_tensor_core_attention_equals_the_plain_kernel(tmp_path, monkey
     assert np.median(rel_err(split, cut)) < 0.02 and rel_err(split, cut).max() < 0.1
 
 
+def test_bfloat16_large_prompt_step_takes_the_64_row_attention_kernel_by_itself(tmp_path, monkeypatch):
+    """A step with query tiles enough for every SM (two prompts of 330 tokens, 16 heads: 4 tokens per 64-row tile) is
+    dispatched to the 64-row kernel without any knob; it must agree with the oracle and with the plain kernel, windows
+    crossing several 32-key tiles and both prompts' first tokens included."""
+    layers = [(latent(heads=16, dim=8, rot_dim=16, vdim=8, kv_rank=48, window=75), None)]
+    cfg, W, d = build(tmp_path, layers, seed=23, q_gain=3.0, width=32)
+    seqs = [toks(330, cfg["vocab"], 24 + i) for i in range(2)]
+    o = oracle_for(cfg, W)
+    want = np.concatenate([o.forward(t) for t in seqs])
+
+    def both(e):
+        rids = [e.feed_open() for _ in seqs]
+        out = e.feed_step([(r, t, list(range(len(t)))) for r, t in zip(rids, seqs)])
+        for r in rids:
+            e.feed_close(r)
+        return out
+
+    with open_engine(d, dtype="bfloat16", max_tokens=1024, max_seqs=2) as e:
+        got = both(e)
+    monkeypatch.setenv("B200_NX_ATTN_MMA", "0")
+    with open_engine(d, dtype="bfloat16", max_tokens=1024, max_seqs=2) as e:
+        plain = both(e)
+    close16(got, want)
+    assert np.median(rel_err(got, plain)) < 0.02 and rel_err(got, plain).max() < 0.1
+
+
 def test_bfloat16_per_expert_tensor_core_path_equals_the_grouped_kernel(tmp_path, monkeypatch):
     """Large steps run every expert's rows as one tensor-core GEMM after reading the row counts back; forced here for
     small steps, including experts that get no token at all."""
