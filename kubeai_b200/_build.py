@@ -30,7 +30,10 @@ SOURCES = [
     "gla.cu",
     "latent_attention.cu",
     "moe.cu",
+    "hyper.cu",
+    "window_attention.cu",
     "nomanex.cu",
+    "zinavik.cu",
     "model_registry.cc",
     "abi_ops.cu",
     "engine.cu",

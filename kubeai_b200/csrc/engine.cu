@@ -1130,12 +1130,14 @@ void Engine::release_blocks(Seq& s) {
 
 // Sliding-window designs: a page whose last token lies before the window of the next token to be computed is never read
 // again by any layer (windows only move forward); it goes back to the pool now instead of when the sequence ends.
+// Pages that hold the first tokens a design keeps visible for ever (cache_keep_first) stay.
 void Engine::trim_window(Seq& s) {
   const int w = model ? model->cache_window() : 0;
   if (w <= 0) return;
+  const int kept_pages = (model->cache_keep_first() + kPage - 1) / kPage;
   const int first_needed = s.n_computed - w + 1;          // oldest position the next token can see
   const int upto = std::min(first_needed / kPage, static_cast<int>(s.blocks.size()));   // pages [0, upto) end before it
-  for (int b = s.n_trimmed; b < upto; ++b) {
+  for (int b = std::max(s.n_trimmed, kept_pages); b < upto; ++b) {
     if (s.blocks[b] >= 0) pool.unref(s.blocks[b]);
     s.blocks[b] = -1;
   }

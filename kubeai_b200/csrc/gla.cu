@@ -27,6 +27,7 @@ __device__ __forceinline__ float ldf(const float* p) { return __ldg(p); }
 __device__ __forceinline__ float ldf(const bf16* p) { return __bfloat162float(__ldg(p)); }
 __device__ __forceinline__ void stf(float* p, float v) { *p = v; }
 __device__ __forceinline__ void stf(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ float siluf_(float x) { return x / (1.0f + expf(-x)); }
 
 constexpr int kRows = 32;      // key rows of the state held by one thread
 constexpr int kGroup = 16;     // tokens staged per shared-memory round (fewer when dim is large)
@@ -78,6 +79,8 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
       S[c][r] = (live[c] && r < rpp && i < D && pos0 > 0) ? Sg[static_cast<long long>(i) * Dv + j[c]] : 0.f;
     }
   const int slice_elems = P * rpp;
+  const bool silu = a.act == GLA_ACT_SILU;
+  const float hdecay = a.head_decay ? a.head_decay[head] : 0.f;   // one constant per head instead of per-channel decays
   for (int g0 = 0; g0 < n; g0 += G) {
     const int gn = min(G, n - g0);
     __syncthreads();
@@ -91,9 +94,11 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
         for (int tt = 0; tt < gn; ++tt) {
           const long long row = static_cast<long long>(tok0 + g0 + tt);
           const T* rp = base + row * a.ld;
-          s3[(tt * 3) * Dp] = ldf(rp + a.q_off + c) * a.q_scale;
-          s3[(tt * 3 + 1) * Dp] = ldf(rp + a.k_off + c);
-          s3[(tt * 3 + 2) * Dp] = __ldg(a.z + row * (a.heads * D) + c);
+          float qv = ldf(rp + a.q_off + c), kv = ldf(rp + a.k_off + c);
+          if (silu) { qv = siluf_(qv); kv = siluf_(kv); }
+          s3[(tt * 3) * Dp] = qv * a.q_scale;
+          s3[(tt * 3 + 1) * Dp] = kv;
+          s3[(tt * 3 + 2) * Dp] = a.head_decay ? hdecay : __ldg(a.z + row * (a.heads * D) + c);
         }
       } else {
         for (int tt = 0; tt < gn; ++tt) { s3[(tt * 3) * Dp] = 0.f; s3[(tt * 3 + 1) * Dp] = 0.f; s3[(tt * 3 + 2) * Dp] = 0.f; }
@@ -101,7 +106,9 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
     }
     for (int e = threadIdx.x; e < gn * cols; e += kThreads) {
       const int tt = e / cols, c = e - tt * cols, jc = blockIdx.x * cols + c;
-      vs[e] = jc < Dv ? ldf(base + static_cast<long long>(tok0 + g0 + tt) * a.ld + a.v_off + head * Dv + jc) : 0.f;
+      float vv = jc < Dv ? ldf(base + static_cast<long long>(tok0 + g0 + tt) * a.ld + a.v_off + head * Dv + jc) : 0.f;
+      if (silu) vv = siluf_(vv);
+      vs[e] = vv;
     }
     __syncthreads();
     for (int tt = 0; tt < gn; ++tt) {
@@ -166,7 +173,41 @@ __global__ void gla_out_gate_kernel(const float* o, const T* g, int ldg, const f
   }
 }
 
+// The general output stage: one warp per (token, head), or per token when the norm runs over the concatenated heads.
+template <typename T>
+__global__ void recurrent_out_gate_kernel(OutGateArgs a, long long units) {
+  const long long p = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (p >= units) return;
+  const int lane = threadIdx.x & 31;
+  const int n = a.joint ? a.heads * a.vdim : a.vdim;        // elements normed together
+  const long long t = a.joint ? p : p / a.heads;
+  const int c0 = a.joint ? 0 : static_cast<int>(p - t * a.heads) * a.vdim;   // first column of the unit in the token's row
+  const float* op = a.o + t * (static_cast<long long>(a.heads) * a.vdim) + c0;
+  const T* g = static_cast<const T*>(a.g) + t * a.ldg + c0;
+  T* y = static_cast<T*>(a.y) + t * a.ldy + c0;
+  float ss = 0.f;
+  for (int i = lane; i < n; i += 32) ss = fmaf(op[i], op[i], ss);
+  for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+  const float inv = 1.0f / sqrtf(ss / static_cast<float>(n) + a.eps);
+  for (int i = lane; i < n; i += 32) {
+    const float gv = ldf(g + i);
+    const float sg = 1.0f / (1.0f + expf(-gv));
+    const float gate = a.gate_act == GATE_SIGMOID ? sg : gv * sg;
+    stf(y + i, op[i] * inv * a.w[i] * gate * a.out_scale);
+  }
+}
+
 }  // namespace
+
+int recurrent_out_gate(const OutGateArgs& a, cudaStream_t st) {
+  const long long units = a.joint ? a.T : static_cast<long long>(a.T) * a.heads;
+  if (units <= 0) return 0;
+  if (!a.o || !a.g || !a.w || !a.y || a.heads < 1 || a.vdim < 1) return -1;
+  const unsigned grid = static_cast<unsigned>((units + 3) / 4);
+  if (a.t == DT_BF16) recurrent_out_gate_kernel<bf16><<<grid, 128, 0, st>>>(a, units);
+  else recurrent_out_gate_kernel<float><<<grid, 128, 0, st>>>(a, units);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 int gla_scan(const GlaArgs& a, cudaStream_t st) {
   if (a.nseq <= 0) return 0;
@@ -190,7 +231,8 @@ int gla_scan(const GlaArgs& a, cudaStream_t st) {
   while (G > 1 && smem_for(G) > 44 * 1024) G >>= 1;
   const size_t smem = smem_for(G);
   if (smem > 48 * 1024) return -1;
-  {
+  if (!a.head_decay) {
+    if (!a.z || !a.z_bias) return -1;
     const long long total = static_cast<long long>(a.T) * a.heads * a.dim;
     if (total > 0) gla_decay_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(a.z, a.z_bias, a.heads * a.dim, a.inv_tau, total);
   }

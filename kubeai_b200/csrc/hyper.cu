@@ -1,0 +1,143 @@
+// Hyper-connections on fp32 residual streams, fused with the RMS norm that feeds the next sublayer (mixers.h HyperArgs),
+// and the scaled embedding that fills the streams.
+//
+// A model with n streams keeps x_1 .. x_n instead of one residual.  A sublayer reads u = sum_s in[s] x_s, and its output
+// y goes back as x_j <- sum_s mix[s, j] x_s + out[j] y, every new stream computed from the old ones.  Between two
+// sublayers the write-back of the first and the read of the second touch the same rows, so one kernel does both: a CTA
+// owns one token row, updates the n streams in place, keeps u in shared memory, reduces mean(u^2) in a fixed order and
+// writes the normed row in the storage type of the projections.  With one stream and no mixing weights the same kernel
+// is the ordinary pre-norm residual step x <- x + y; h = rmsnorm(x).  Everything is fp32 up to the single rounding of h.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "mixers.h"
+
+namespace b200 {
+namespace {
+
+typedef __nv_bfloat16 bf16;
+constexpr int kMaxStreams = 8;
+__device__ __forceinline__ float ldf(const float* p) { return *p; }
+__device__ __forceinline__ float ldf(const bf16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stf(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <typename TW>
+__global__ void embed_scaled_kernel(const TW* embed, const int* ids, float* x, int W, int vocab, float scale, int streams, long long stride) {
+  const long long t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const TW* e = embed + static_cast<long long>(id) * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = ldf(e + i) * scale;
+    for (int s = 0; s < streams; ++s) x[s * stride + t * W + i] = v;
+  }
+}
+
+template <typename TY, typename TH>
+__global__ void hyper_step_kernel(HyperArgs a) {
+  extern __shared__ float us[];   // [W] the sublayer input before the norm
+  __shared__ float red[32];
+  __shared__ float coef[kMaxStreams * kMaxStreams + 2 * kMaxStreams];
+  const int r = blockIdx.x, n = a.streams;
+  const long long t = a.row_index ? a.row_index[r] : r;
+  float* mixs = coef;
+  float* outs = coef + kMaxStreams * kMaxStreams;
+  float* ins = outs + kMaxStreams;
+  if (threadIdx.x < n * n) mixs[threadIdx.x] = a.mix ? a.mix[threadIdx.x] : (threadIdx.x / n == threadIdx.x % n ? 1.f : 0.f);
+  if (threadIdx.x < n) {
+    outs[threadIdx.x] = a.out ? a.out[threadIdx.x] : 1.f;
+    ins[threadIdx.x] = a.in ? a.in[threadIdx.x] : 1.f;
+  }
+  __syncthreads();
+  const TY* y = static_cast<const TY*>(a.y);
+  const bool plain = !a.mix;   // identity mixing: x_j + out[j] y exactly, without the multiplications by 0 and 1
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < a.W; i += blockDim.x) {
+    float xs[kMaxStreams];
+#pragma unroll
+    for (int s = 0; s < kMaxStreams; ++s)
+      if (s < n) xs[s] = a.x[s * a.stream_stride + t * a.W + i];
+    if (y) {
+      const float yv = ldf(y + t * a.W + i);
+      float nx[kMaxStreams];
+#pragma unroll
+      for (int j = 0; j < kMaxStreams; ++j) {
+        if (j < n) {
+          float acc;
+          if (plain) acc = xs[j];
+          else {
+            acc = 0.f;
+#pragma unroll
+            for (int s = 0; s < kMaxStreams; ++s)
+              if (s < n) acc = fmaf(mixs[s * n + j], xs[s], acc);
+          }
+          nx[j] = fmaf(outs[j], yv, acc);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kMaxStreams; ++j)
+        if (j < n) { xs[j] = nx[j]; a.x[j * a.stream_stride + t * a.W + i] = nx[j]; }
+    }
+    if (a.h) {
+      float u = 0.f;
+      if (a.in) {
+#pragma unroll
+        for (int s = 0; s < kMaxStreams; ++s)
+          if (s < n) u = fmaf(ins[s], xs[s], u);
+      } else {
+#pragma unroll
+        for (int s = 0; s < kMaxStreams; ++s)
+          if (s < n) u += xs[s];
+      }
+      us[i] = u;
+      ss = fmaf(u, u, ss);
+    }
+  }
+  if (!a.h) return;
+  TH* h = static_cast<TH*>(a.h) + static_cast<long long>(r) * a.W;
+  if (!a.norm_w) {
+    for (int i = threadIdx.x; i < a.W; i += blockDim.x) stf(h + i, us[i]);   // each thread reads back what it wrote
+    return;
+  }
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
+  if (lane == 0) red[wrp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];   // warps in a fixed order, the same in every thread
+  const float inv = 1.0f / sqrtf(tot / static_cast<float>(a.W) + a.eps);
+  for (int i = threadIdx.x; i < a.W; i += blockDim.x) stf(h + i, us[i] * inv * a.norm_w[i]);
+}
+
+inline int threads_for(int W) { return W >= 2048 ? 256 : (W >= 256 ? 128 : 64); }
+
+}  // namespace
+
+int embed_scaled(const void* embed, DType tw, const int* ids, float* x, int T, int W, int vocab, float scale, int streams,
+                 long long stream_stride, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (W < 1 || streams < 1) return -1;
+  if (tw == DT_BF16) embed_scaled_kernel<bf16><<<T, threads_for(W), 0, st>>>(static_cast<const bf16*>(embed), ids, x, W, vocab, scale, streams, stream_stride);
+  else embed_scaled_kernel<float><<<T, threads_for(W), 0, st>>>(static_cast<const float*>(embed), ids, x, W, vocab, scale, streams, stream_stride);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int hyper_step(const HyperArgs& a, cudaStream_t st) {
+  if (a.rows <= 0) return 0;
+  if (!a.x || a.streams < 1 || a.streams > kMaxStreams || a.W < 1) return -1;
+  if (a.y && a.row_index) return -1;   // an update of chosen rows only would leave the streams inconsistent
+  const size_t smem = a.h ? static_cast<size_t>(a.W) * sizeof(float) : 0;
+  if (smem > 48 * 1024) return -1;
+  const int th = threads_for(a.W);
+#define HS(TY, TH) hyper_step_kernel<TY, TH><<<a.rows, th, smem, st>>>(a)
+  const bool y16 = a.y && a.ty == DT_BF16, h16 = a.h && a.th == DT_BF16;
+  if (y16 && h16) HS(bf16, bf16);
+  else if (y16) HS(bf16, float);
+  else if (h16) HS(float, bf16);
+  else HS(float, float);
+#undef HS
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+}  // namespace b200

@@ -100,10 +100,11 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(LinearArgs a) {
     const int t = row0 + ty * 4 + i;
     if (t >= a.T) continue;
     if (a.x_rows && a.x_rows[t] < 0) continue;
+    const float rs = a.row_scale ? a.row_scale[t] : 1.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = col0 + tx * 4 + j;
-      if (n < a.N) st1(Y + static_cast<long long>(t) * a.ldy + n, apply_act(acc[i][j], a.act));
+      if (n < a.N) st1(Y + static_cast<long long>(t) * a.ldy + n, apply_act(a.row_scale ? acc[i][j] * rs : acc[i][j], a.act));
     }
   }
 }
@@ -214,12 +215,13 @@ __global__ void __launch_bounds__(256) linear_tile_mma_kernel(LinearArgs a) {
     const int t = row0 + 16 * wm + g + 8 * half;
     if (t >= a.T) continue;
     if (a.x_rows && a.x_rows[t] < 0) continue;
+    const float rs = a.row_scale ? a.row_scale[t] : 1.f;
 #pragma unroll
     for (int nb = 0; nb < 4; ++nb)
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int n = col0 + 32 * wn + 8 * nb + 2 * t4 + j;
-        if (n < a.N) st1(Y + static_cast<long long>(t) * a.ldy + n, apply_act(acc[nb][2 * half + j], a.act));
+        if (n < a.N) st1(Y + static_cast<long long>(t) * a.ldy + n, apply_act(a.row_scale ? acc[nb][2 * half + j] * rs : acc[nb][2 * half + j], a.act));
       }
   }
 }
@@ -257,7 +259,7 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(LinearArgs a) {
       float v = acc[t];
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      if (lane == 0) st1(Y + static_cast<long long>(t) * a.ldy + n, apply_act(v, a.act));
+      if (lane == 0) st1(Y + static_cast<long long>(t) * a.ldy + n, apply_act(a.row_scale ? v * a.row_scale[t] : v, a.act));
     }
   }
 }
@@ -283,7 +285,7 @@ __global__ void __launch_bounds__(256) linear_picked_rows_kernel(LinearArgs a, P
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) st1(static_cast<TY*>(a.Y) + dst * a.ldy + n, apply_act(acc, a.act));
+  if (lane == 0) st1(static_cast<TY*>(a.Y) + dst * a.ldy + n, apply_act(a.row_scale ? acc * a.row_scale[r] : acc, a.act));
 }
 
 template <typename TX, typename TW, typename TY>

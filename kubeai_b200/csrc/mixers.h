@@ -1,7 +1,10 @@
 // Host launchers of the kernels behind the non-Llama model designs: a shape-agnostic linear layer (plain, batched per
 // head, or grouped per expert), Dynamic-Tanh norm fused with the fp32 residual update, a hashed bigram embedding,
-// gated linear attention (decayed outer-product state per sequence slot), latent attention (paged low-rank KV with a
-// shared rotated key and a sliding window), group-limited expert routing, and the gated activations they use.
+// gated linear attention (decayed outer-product state per sequence slot; per-channel learned decays or one constant per
+// head), latent attention (paged low-rank KV with a shared rotated key and a sliding window), softmax attention over
+// paged keys and values with grouped heads, a sliding window and kept first tokens, hyper-connections (several residual
+// streams read and written through small mixing weights) with RMS norm, expert routing (softmax or sigmoid scores,
+// optionally group-limited), and the gated activations they use.
 //
 // Storage type: every activation / weight matrix is either bf16 or fp32 (DType); the residual stream, recurrent
 // states, router scores, decays, softmax and norm statistics are always fp32.  All pointers are device pointers.
@@ -23,6 +26,8 @@ enum LinearAct { LIN_NONE = 0, LIN_RELU2 = 1 };   // epilogue on the fp32 accumu
 //   x_rows (optional): row(t) = x_rows[t], a negative entry reads a zero row and its output row is not written.
 //   tile_group (optional, needs T % 64 == 0 capacity): rows [64 i, 64 i + 64) use weight matrix W + tile_group[i] * wbs;
 //     a negative entry skips the tile (expert-grouped rows padded to the tile size).
+//   row_scale (optional, fp32): the accumulator of row t is multiplied by row_scale[t] before act, which is the product
+//     of the scaled input row, (s x) W^T = s (x W^T), without a scaled copy of x.
 // The accumulation order of one output element never depends on T or on the other rows (k ascending inside a tile
 // kernel, a fixed lane pattern in the few-row kernel), so a row's result does not depend on what shares the batch.
 struct LinearArgs {
@@ -34,14 +39,15 @@ struct LinearArgs {
   const int* x_rows;
   const int* tile_group;
   int act;
+  const float* row_scale;
 };
 inline LinearArgs linear_args(const void* X, DType tx, const void* W, DType tw, void* Y, DType ty, int T, int N, int K) {
-  LinearArgs a = {X, W, Y, tx, tw, ty, T, N, K, K, K, N, 1, 0, 0, 0, nullptr, nullptr, LIN_NONE};
+  LinearArgs a = {X, W, Y, tx, tw, ty, T, N, K, K, K, N, 1, 0, 0, 0, nullptr, nullptr, LIN_NONE, nullptr};
   return a;
 }
 int linear(const LinearArgs& a, cudaStream_t st);
 // `rows` rows (a handful: the expert choices of a decode step), row r reading X row src_rows[r] (or r / src_div), writing Y row
-// dst_rows[r], with weight matrix W + groups[r] * wbs; a.T, a.batch, x_rows and tile_group are not used.
+// dst_rows[r], with weight matrix W + groups[r] * wbs (row_scale[r] applies); a.T, a.batch, x_rows and tile_group are not used.
 struct PickedRows {
   int rows;
   const int* src_rows; int src_div;
@@ -75,6 +81,10 @@ int argmax_f32(const float* logits, int* out, int S, int V, cudaStream_t st);
 // v_off; heads x dim, heads x dim, heads x vdim).  z: fp32 [T, heads * dim] pre-activations, replaced by the decays.  states: fp32 [slot][heads][dim][vdim].
 // seqs: int [nseq][8] = {first row, rows, first position, state slot, ...}; a sequence whose first position is 0 starts
 // from a zero state whatever its slot held.  o: fp32 [T, heads * vdim].
+// head_decay (optional, fp32 [heads]): every key channel of head h decays by the constant head_decay[h] (the scalar-decay
+// linear attention, S <- lambda_h S + k v^T); z and z_bias are then unused and may be null.  act: GLA_ACT_SILU applies
+// x * sigmoid(x) to q, k and v as they are read (q before q_scale).
+enum GlaAct { GLA_ACT_NONE = 0, GLA_ACT_SILU = 1 };
 struct GlaArgs {
   const void* qkv; DType t; int ld, q_off, k_off, v_off;
   float* z; const float* z_bias; float inv_tau, q_scale;   // z is overwritten with the decays
@@ -82,11 +92,24 @@ struct GlaArgs {
   float* states; const int* seqs; int nseq;
   int heads, dim, vdim;
   float* o;
+  const float* head_decay = nullptr;
+  int act = GLA_ACT_NONE;
 };
 int gla_scan(const GlaArgs& a, cudaStream_t st);
 // y[t, h * vdim + :] (leading dimension ldy) = o[t, h, :] / sqrt(mean(o^2) + eps) * w * silu(g[t, h, :])   (w: fp32 [vdim], shared by the heads)
 int gla_out_gate(const float* o, const void* g, int ldg, const float* w, float eps, void* y, int ldy, DType t, int T, int heads, int vdim,
                  cudaStream_t st);
+// The general form: the unit-RMS norm runs per head over vdim with w [vdim] shared by the heads (joint = false) or once
+// over the token's concatenated heads with w [heads * vdim] (joint = true); the gate is silu(g) or sigmoid(g); the result
+// is multiplied by out_scale before it is rounded to the storage type.
+enum GateAct { GATE_SILU = 0, GATE_SIGMOID = 1 };
+struct OutGateArgs {
+  const float* o; const void* g; int ldg; const float* w; float eps;
+  void* y; int ldy; DType t;
+  int T, heads, vdim;
+  bool joint; int gate_act; float out_scale;
+};
+int recurrent_out_gate(const OutGateArgs& a, cudaStream_t st);
 
 // ---------------------------------------------------------------- latent attention (latent_attention.cu)
 // Rotation table for interleaved pairs (2i, 2i+1): cs[p][i] = (cos, sin)(p * base^(-2i/dims)), computed in double.
@@ -117,20 +140,83 @@ struct LatentAttnArgs {
 };
 int latent_attention(const LatentAttnArgs& a, cudaStream_t st);
 
+// ---------------------------------------------------------------- softmax attention, windowed with kept first tokens (window_attention.cu)
+// Rotation table for interleaved pairs with YaRN-style frequency scaling: f_i = base^(-2i/dims) is blended towards
+// f_i / factor by a ramp between the pair indices at which `fast` and `slow` rotations fit into `original` positions,
+// and cos and sin are multiplied by 0.1 ln(factor) + 1.  yarn == nullptr gives the plain table.  Computed in double.
+struct RopeYarn { double factor, original, fast, slow; };
+int rope_table_yarn(float2* table, int max_pos, int dims, double base, const RopeYarn* yarn, cudaStream_t st);
+// Per token: the first rot_dims dimensions of every query head (heads x dim at q) and key head (kv_heads x dim at k) are
+// rotated by the token's position (pairs (2i, 2i+1)), then each head is divided by its root mean square over dim (eps
+// inside the root; unit_norm = false skips that).  Queries go to qn (fp32 [T, heads * dim]); keys and values
+// (kv_heads x vdim at v) go to the token's cache row: cache [slot][kv_heads * dim | kv_heads * vdim] of type t.
+struct QkPrepArgs {
+  const void* q; const void* k; const void* v; int ld; DType t;   // column blocks of one row-major buffer
+  const float2* rope; int rot_dims;
+  bool unit_norm; float eps;
+  const int* positions; const int* slots;
+  float* qn; void* cache;
+  int T, heads, kv_heads, dim, vdim;
+};
+int qk_rope_norm_cache(const QkPrepArgs& a, cudaStream_t st);
+// Softmax attention of token t (position p of its sequence) over the cached keys j <= p with p - j < window or
+// j < keep_first (kept tokens stay at their own positions).  Query head h reads key/value head h / (heads / kv_heads).
+// score = qn . k * scale, softmax in fp32.  y[t, h * vdim + :] = out_scale * o * sigmoid(gate[t, h * vdim + :]) (gate of
+// type t with leading dimension ldg, may be null: no gate), rounded once to type t (leading dimension ldy).
+struct WindowAttnArgs {
+  const float* qn; const void* cache; DType t;
+  const int* positions; const int* seq_of_tok; const int* block_tables; int max_blocks, page;
+  const void* gate; int ldg; float out_scale;
+  void* y; int ldy;
+  int T, heads, kv_heads, dim, vdim, window, keep_first; float scale;
+  const int* seqs; int nseq; int max_ctx;
+};
+int window_attention(const WindowAttnArgs& a, cudaStream_t st);
+
+// ---------------------------------------------------------------- hyper-connections, RMS norm (hyper.cu)
+// x[s][t] = embed[ids[t]] * scale for every stream s (fp32; stream s starts at x + s * stream_stride).
+int embed_scaled(const void* embed, DType tw, const int* ids, float* x, int T, int W, int vocab, float scale, int streams,
+                 long long stream_stride, cudaStream_t st);
+// One boundary between two sublayers on `streams` fp32 residual streams (1..8).  For r < rows, t = row_index ? row_index[r] : r:
+//   if (y)  all streams at once from the old ones: x_j[t] <- sum_s mix[s * streams + j] * x_s[t] + out[j] * y[t]
+//           (mix null: identity; out null: ones; with one stream and both null this is the plain residual sum)
+//   u = sum_s in[s] * x_s[t]                                   (in null: the plain sum of the streams)
+//   if (h)  h[r] = norm_w ? u / sqrt(mean(u^2) + eps) * norm_w : u      (fp32 statistics; h of type th)
+struct HyperArgs {
+  float* x; int streams; long long stream_stride;
+  const void* y; DType ty;
+  const float* mix; const float* out; const float* in;
+  const float* norm_w; float eps;
+  void* h; DType th;
+  const int* row_index; int rows; int W;
+};
+int hyper_step(const HyperArgs& a, cudaStream_t st);
+
 // ---------------------------------------------------------------- mixture of experts (moe.cu)
 // scores: fp32 [T, E] router logits in, clobbered.  softmax over E; experts form `groups` equal groups of neighbours, a
 // group's score is its largest member, only the `keep` best groups are eligible; the `top` largest eligible scores are
 // chosen (ties: lower index) and used unchanged as weights.  topk_ids / topk_w: [T, top].
-int moe_route(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, cudaStream_t st);
+// score_fn: MOE_SOFTMAX as above, MOE_SIGMOID scores every expert by sigmoid(z) on its own (no normalisation over E).
+enum MoeScore { MOE_SOFTMAX = 0, MOE_SIGMOID = 1 };
+int moe_route(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, cudaStream_t st,
+              int score_fn = MOE_SOFTMAX);
 // Sort the T * top (token, choice) pairs by expert into 64-row tiles: sorted_rows[cap] = token of each sorted row or -1,
 // tile_group[cap / 64] = expert of each tile or -1, pair_pos[T * top] = sorted row of each pair.  cap >= T*top + E*64.
 // expert_rows (optional): [E][2] = {first sorted row, rows} of every expert.
+// topk_w with sorted_w (optional): sorted_w[cap] = the router weight of each sorted row (0 for padding), for designs that
+// scale an expert's input instead of its output.
 int moe_align(const int* topk_ids, int T, int top, int E, int* sorted_rows, int* tile_group, int* pair_pos, int cap, cudaStream_t st,
-              int* expert_rows = nullptr);
+              int* expert_rows = nullptr, const float* topk_w = nullptr, float* sorted_w = nullptr);
 // out[t] = sum_k topk_w[t, k] * y[pair_pos[t * top + k]]   (y [cap, W] fp32 or bf16, k ascending)
 int moe_combine(const void* y, DType ty, const int* pair_pos, const float* topk_w, void* out, DType t, int T, int top, int W, cudaStream_t st);
-// bf16 helpers of the per-expert tensor-core path: x rows in sorted order (negative source row -> zeros), max(p, 0)^2 in place
-int moe_gather_bf16(const void* x, const int* sorted_rows, void* out, int rows, int W, cudaStream_t st);
+// out[t] = sum_k w[t, k] * y[pair_pos[t * top + k]] + sigmoid(add_gate[t * ld_gate]) * add[t]: the routed experts plus a
+// shared expert behind a per-token gate.  topk_w may be null (every weight 1: the weight was applied to the expert's
+// input); add ([T, W]) and add_gate are of type t, add_gate may be null (gate 1), add may be null (no shared expert).
+int moe_combine_add(const void* y, DType ty, const int* pair_pos, const float* topk_w, const void* add, const void* add_gate, int ld_gate,
+                    void* out, DType t, int T, int top, int W, cudaStream_t st);
+// bf16 helpers of the per-expert tensor-core path: x rows in sorted order (negative source row -> zeros; with row_scale the
+// row is multiplied by row_scale[r] in fp32 and rounded once), max(p, 0)^2 in place
+int moe_gather_bf16(const void* x, const int* sorted_rows, void* out, int rows, int W, cudaStream_t st, const float* row_scale = nullptr);
 int relu2_bf16(void* p, long long n, cudaStream_t st);
 
 }  // namespace b200

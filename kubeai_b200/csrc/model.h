@@ -61,6 +61,8 @@ class Model {
   // the most tokens back any caching layer looks (itself included); 0 = some layer sees the whole sequence.  The engine
   // returns pages that lie wholly before every such window to the pool while the sequence is still running.
   virtual int cache_window() const { return 0; }
+  // the first tokens of a sequence that stay visible to every later token whatever the window: their pages are not returned
+  virtual int cache_keep_first() const { return 0; }
   // allocate weights (unset), activations for env.Tcap tokens, caches for env.num_blocks pages, states for env.num_slots
   virtual int init(const ModelEnv& env) = 0;
   // sizes that only the checkpoint's tensor shapes give; called before init() when there is a checkpoint
@@ -106,5 +108,6 @@ int engine_create_with_model(const b200_config* cfg, std::unique_ptr<Model> mdl,
 Model* engine_model(b200_engine* e);
 
 std::unique_ptr<Model> make_nomanex(const JVal& config, DType dtype, std::string* err);
+std::unique_ptr<Model> make_zinavik(const JVal& config, DType dtype, std::string* err);
 
 }  // namespace b200

@@ -11,6 +11,7 @@ struct Entry {
 };
 const Entry kModels[] = {
     {"Nomanex", make_nomanex},
+    {"Zinavik", make_zinavik},
 };
 }  // namespace
 

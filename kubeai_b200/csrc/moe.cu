@@ -17,19 +17,23 @@ namespace {
 typedef __nv_bfloat16 bf16;
 
 // one warp per token; scores row in global memory is the scratch (chosen entries are overwritten with -1)
-__global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top) {
+__global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, int score_fn) {
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
   const int lane = threadIdx.x & 31;
   float* s = scores + static_cast<long long>(t) * E;
-  float mx = -FLT_MAX;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
-  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) { const float v = expf(s[e] - mx); s[e] = v; sum += v; }
-  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  const float inv = 1.0f / sum;
-  for (int e = lane; e < E; e += 32) s[e] *= inv;
+  if (score_fn == MOE_SIGMOID) {
+    for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
+  } else {
+    float mx = -FLT_MAX;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) { const float v = expf(s[e] - mx); s[e] = v; sum += v; }
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < E; e += 32) s[e] *= inv;
+  }
   __syncwarp();
   const int per = E / groups;
   // keep the best groups: bit g of `kept` (lane-uniform); groups <= 64
@@ -75,13 +79,13 @@ __global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, in
 
 // single CTA: histogram, padded offsets, scatter
 __global__ void __launch_bounds__(1024) moe_align_kernel(const int* topk_ids, int pairs, int top, int E, int* sorted_rows, int* tile_group,
-                                                         int* pair_pos, int cap, int* expert_rows) {
+                                                         int* pair_pos, int cap, int* expert_rows, const float* topk_w, float* sorted_w) {
   extern __shared__ int sh[];   // count[E], start[E + 1], fill[E]
   int* count = sh;
   int* start = sh + E;
   int* fill = sh + 2 * E + 1;
   for (int e = threadIdx.x; e < E; e += blockDim.x) { count[e] = 0; fill[e] = 0; }
-  for (int i = threadIdx.x; i < cap; i += blockDim.x) sorted_rows[i] = -1;
+  for (int i = threadIdx.x; i < cap; i += blockDim.x) { sorted_rows[i] = -1; if (sorted_w) sorted_w[i] = 0.f; }
   for (int i = threadIdx.x; i < cap / 64; i += blockDim.x) tile_group[i] = -1;
   __syncthreads();
   for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[topk_ids[p]], 1);
@@ -103,6 +107,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* topk_ids, in
     const int r = start[e] + atomicAdd(&fill[e], 1);
     sorted_rows[r] = p / top;
     pair_pos[p] = r;
+    if (sorted_w) sorted_w[r] = topk_w[p];
   }
 }
 
@@ -110,11 +115,18 @@ __device__ __forceinline__ float ldy(const float* p) { return *p; }
 __device__ __forceinline__ float ldy(const bf16* p) { return __bfloat162float(*p); }
 
 template <typename T, typename TYIN>
-__global__ void moe_combine_kernel(const TYIN* y, const int* pair_pos, const float* topk_w, T* out, int top, int W) {
+__global__ void moe_combine_kernel(const TYIN* y, const int* pair_pos, const float* topk_w, T* out, int top, int W, const T* add = nullptr,
+                                   const T* add_gate = nullptr, int ld_gate = 0) {
   const long long t = blockIdx.x;
+  float gate = 1.f;
+  if (add && add_gate) gate = 1.0f / (1.0f + expf(-ldy(add_gate + t * ld_gate)));
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     float acc = 0.f;
-    for (int k = 0; k < top; ++k) acc = fmaf(topk_w[t * top + k], ldy(y + static_cast<long long>(pair_pos[t * top + k]) * W + i), acc);
+    for (int k = 0; k < top; ++k) {
+      const float yv = ldy(y + static_cast<long long>(pair_pos[t * top + k]) * W + i);
+      acc = topk_w ? fmaf(topk_w[t * top + k], yv, acc) : acc + yv;
+    }
+    if (add) acc = fmaf(gate, ldy(add + t * W + i), acc);
     if (sizeof(T) == 2) reinterpret_cast<bf16*>(out)[t * W + i] = __float2bfloat16_rn(acc);
     else reinterpret_cast<float*>(out)[t * W + i] = acc;
   }
@@ -122,20 +134,20 @@ __global__ void moe_combine_kernel(const TYIN* y, const int* pair_pos, const flo
 
 }  // namespace
 
-int moe_route(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, cudaStream_t st) {
+int moe_route(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, cudaStream_t st, int score_fn) {
   if (T <= 0) return 0;
   if (E < 1 || groups < 1 || groups > 64 || E % groups || keep < 1 || keep > groups || top < 1 || top > keep * (E / groups)) return -1;
-  moe_route_kernel<<<(T + 3) / 4, 128, 0, st>>>(scores, topk_ids, topk_w, T, E, groups, keep, top);
+  moe_route_kernel<<<(T + 3) / 4, 128, 0, st>>>(scores, topk_ids, topk_w, T, E, groups, keep, top, score_fn);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 int moe_align(const int* topk_ids, int T, int top, int E, int* sorted_rows, int* tile_group, int* pair_pos, int cap, cudaStream_t st,
-              int* expert_rows) {
+              int* expert_rows, const float* topk_w, float* sorted_w) {
   if (T <= 0) return 0;
-  if (cap % 64 || cap < T * top + E * 64) return -1;
+  if (cap % 64 || cap < T * top + E * 64 || (sorted_w && !topk_w)) return -1;
   const size_t smem = static_cast<size_t>(3 * E + 1) * sizeof(int);
   if (smem > 48 * 1024) return -1;
-  moe_align_kernel<<<1, 1024, smem, st>>>(topk_ids, T * top, top, E, sorted_rows, tile_group, pair_pos, cap, expert_rows);
+  moe_align_kernel<<<1, 1024, smem, st>>>(topk_ids, T * top, top, E, sorted_rows, tile_group, pair_pos, cap, expert_rows, topk_w, sorted_w);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -150,15 +162,43 @@ int moe_combine(const void* y, DType ty, const int* pair_pos, const float* topk_
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
+int moe_combine_add(const void* y, DType ty, const int* pair_pos, const float* topk_w, const void* add, const void* add_gate, int ld_gate,
+                    void* out, DType t, int T, int top, int W, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (!y || !pair_pos || !out || top < 1 || (ty == DT_BF16 && t != DT_BF16)) return -1;
+  const int th = W >= 1024 ? 256 : 128;
+  if (ty == DT_BF16)
+    moe_combine_kernel<bf16, bf16><<<T, th, 0, st>>>(static_cast<const bf16*>(y), pair_pos, topk_w, static_cast<bf16*>(out), top, W,
+                                                       static_cast<const bf16*>(add), static_cast<const bf16*>(add_gate), ld_gate);
+  else if (t == DT_BF16)
+    moe_combine_kernel<bf16, float><<<T, th, 0, st>>>(static_cast<const float*>(y), pair_pos, topk_w, static_cast<bf16*>(out), top, W,
+                                                        static_cast<const bf16*>(add), static_cast<const bf16*>(add_gate), ld_gate);
+  else
+    moe_combine_kernel<float, float><<<T, th, 0, st>>>(static_cast<const float*>(y), pair_pos, topk_w, static_cast<float*>(out), top, W,
+                                                         static_cast<const float*>(add), static_cast<const float*>(add_gate), ld_gate);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 namespace {
 // rows of x in expert-sorted order (16-byte pieces; W % 8 == 0): a negative source row becomes zeros
-__global__ void moe_gather_kernel(const uint4* x, const int* sorted_rows, uint4* out, int pieces, long long total) {
+__global__ void moe_gather_kernel(const uint4* x, const int* sorted_rows, uint4* out, int pieces, long long total, const float* row_scale) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const long long r = i / pieces;
   const int c = static_cast<int>(i - r * pieces);
   const int src = sorted_rows[r];
-  out[i] = src < 0 ? make_uint4(0, 0, 0, 0) : x[static_cast<long long>(src) * pieces + c];
+  uint4 v = src < 0 ? make_uint4(0, 0, 0, 0) : x[static_cast<long long>(src) * pieces + c];
+  if (row_scale && src >= 0) {
+    const float s = row_scale[r];
+    uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const __nv_bfloat162 o = __floats2bfloat162_rn(__uint_as_float(u[k] << 16) * s, __uint_as_float(u[k] & 0xffff0000u) * s);
+      u[k] = *reinterpret_cast<const uint32_t*>(&o);
+    }
+    v = make_uint4(u[0], u[1], u[2], u[3]);
+  }
+  out[i] = v;
 }
 __global__ void relu2_kernel(__nv_bfloat162* p, long long n2) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -169,11 +209,11 @@ __global__ void relu2_kernel(__nv_bfloat162* p, long long n2) {
 }
 }  // namespace
 
-int moe_gather_bf16(const void* x, const int* sorted_rows, void* out, int rows, int W, cudaStream_t st) {
+int moe_gather_bf16(const void* x, const int* sorted_rows, void* out, int rows, int W, cudaStream_t st, const float* row_scale) {
   if (rows <= 0) return 0;
   if (W % 8) return -1;
   const long long total = static_cast<long long>(rows) * (W / 8);
-  moe_gather_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(static_cast<const uint4*>(x), sorted_rows, static_cast<uint4*>(out), W / 8, total);
+  moe_gather_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(static_cast<const uint4*>(x), sorted_rows, static_cast<uint4*>(out), W / 8, total, row_scale);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
