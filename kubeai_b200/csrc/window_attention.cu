@@ -12,7 +12,8 @@
 // size, bf16 or fp32 cache: one CTA per (token, head), four warps share the token's keys in 32-key chunks, a lane owns
 // one key for the scores and a slice of the value columns for the output, online softmax in fp32, the warps' partial
 // results meet in shared memory in a fixed order; the sigmoid output gate and the branch scale are applied before the
-// single rounding to the storage type).
+// single rounding to the storage type), and `window_attn_mma_kernel` (bf16, head sizes that fit the mma.sync fragments:
+// 64 query rows of one sequence, the heads of one key/value group together, against 64-key tiles on the tensor cores).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <float.h>
@@ -22,6 +23,7 @@
 #include <algorithm>
 #include <vector>
 
+#include "launch.h"
 #include "mixers.h"
 
 namespace b200 {
@@ -94,7 +96,7 @@ __global__ void __launch_bounds__(128) qk_prep_kernel(QkPrepArgs a) {
 }
 
 // ---------------------------------------------------------------------------------------------- attention, any head size
-constexpr int kWarps = 4;
+constexpr int kWarps = 4, kWarpsDecode = 16;
 constexpr int kMaxVR = 8;   // value columns per lane: vdim <= 256
 
 template <typename T>
@@ -124,11 +126,11 @@ __device__ __forceinline__ float dot_row(const float* q, const T* k, int D, bool
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kWarps * 32) window_attn_kernel(WindowAttnArgs a, bool vec) {
+__global__ void __launch_bounds__(kWarpsDecode * 32) window_attn_kernel(WindowAttnArgs a, bool vec) {
   extern __shared__ float sm[];   // q [dim] | per warp: m, l, acc [vdim]
   const long long t = blockIdx.x / a.heads;
   const int h = blockIdx.x % a.heads;
-  const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int D = a.dim, Dv = a.vdim;
   const int g = h / (a.heads / a.kv_heads);
   const int p = a.positions[t];
@@ -146,7 +148,7 @@ __global__ void __launch_bounds__(kWarps * 32) window_attn_kernel(WindowAttnArgs
   float m = -FLT_MAX, l = 0.f, acc[kMaxVR];
 #pragma unroll
   for (int r = 0; r < kMaxVR; ++r) acc[r] = 0.f;
-  for (int c0 = wrp * 32; c0 < n; c0 += kWarps * 32) {
+  for (int c0 = wrp * 32; c0 < n; c0 += nwarps * 32) {
     const int i = c0 + lane;
     long long row = -1;
     float s = -FLT_MAX;
@@ -188,10 +190,14 @@ __global__ void __launch_bounds__(kWarps * 32) window_attn_kernel(WindowAttnArgs
   }
   __syncthreads();
   float mm = -FLT_MAX;
-  for (int w = 0; w < kWarps; ++w) mm = fmaxf(mm, part[w * (Dv + 2)]);
+  for (int w = 0; w < nwarps; ++w) mm = fmaxf(mm, part[w * (Dv + 2)]);
   float ll = 0.f;
-  float f[kWarps];
-  for (int w = 0; w < kWarps; ++w) {
+  float f[kWarpsDecode];
+#pragma unroll
+  for (int w = 0; w < kWarpsDecode; ++w) f[w] = 0.f;
+#pragma unroll
+  for (int w = 0; w < kWarpsDecode; ++w) {
+    if (w >= nwarps) break;
     const float pm = part[w * (Dv + 2)];
     f[w] = pm == -FLT_MAX ? 0.f : expf(pm - mm);
     ll = fmaf(part[w * (Dv + 2) + 1], f[w], ll);
@@ -201,10 +207,222 @@ __global__ void __launch_bounds__(kWarps * 32) window_attn_kernel(WindowAttnArgs
   T* y = static_cast<T*>(a.y) + t * a.ldy + static_cast<long long>(h) * Dv;
   for (int c = threadIdx.x; c < Dv; c += blockDim.x) {
     float o = 0.f;
-    for (int w = 0; w < kWarps; ++w) o = fmaf(part[w * (Dv + 2) + 2 + c], f[w], o);
+#pragma unroll
+    for (int w = 0; w < kWarpsDecode; ++w)
+      if (w < nwarps) o = fmaf(part[w * (Dv + 2) + 2 + c], f[w], o);
     o *= inv;
     if (gate) o *= sigmoidf_(ldf(gate + t * a.ldg + static_cast<long long>(h) * Dv + c));
     stf(y + c, o * a.out_scale);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- attention on the tensor cores
+// bf16 cache, dim % 16 == 0, vdim % 16 == 0, both <= 128.  A CTA of four warps owns 64 query rows of one sequence: TQ = 64 / gs
+// consecutive tokens times the gs query heads that share one key/value head (gs = heads / kv_heads when that divides 64,
+// else 1 and every query head is its own group), so one key/value tile in shared memory serves the whole group.  Keys
+// come in tiles of 64 from the pages by cp.async, two buffers; first the kept first tokens that lie before the tile's
+// lowest window, then the window itself.  S = Q K^T and O += P V are mma.sync m16n8k16 products with fp32 accumulators;
+// the mask (j <= p, p - j < window or j < keep_first, per row), the scale and the online softmax work on the score
+// fragments in registers, a row's four lanes share its maximum by shuffles.  P is rounded to bf16 for the second product.
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+constexpr int kTileRows = 64, kTileKeys = 64;
+constexpr float kMasked = -1e30f;
+
+template <int NV>   // value n-tiles of 8 columns held per thread: vdim <= 8 * NV
+__global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnArgs a, int gs, int TQ) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int D = a.dim, Dv = a.vdim, LDK = D + 8, LDV = Dv + 8;
+  bf16* Qs = reinterpret_cast<bf16*>(smraw);                 // [64][LDK]
+  bf16* Ks = Qs + kTileRows * LDK;                           // [2][64][LDK]
+  bf16* Vs = Ks + 2 * kTileKeys * LDK;                       // [2][64][LDV]
+  const int tid = threadIdx.x, lane = tid & 31, wrp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+  // which sequence and which tile of it
+  int tile = blockIdx.x, s = 0, n = 0;
+  for (; s < a.nseq; ++s) {
+    n = a.seqs[s * 8 + 1];
+    const int nt = (n + TQ - 1) / TQ;
+    if (tile < nt) break;
+    tile -= nt;
+  }
+  if (s >= a.nseq) return;
+  const int tok0 = a.seqs[s * 8] + tile * TQ, ntq = min(TQ, n - tile * TQ);
+  const int p0 = a.seqs[s * 8 + 2] + tile * TQ, p1 = p0 + ntq - 1;
+  const int hy = blockIdx.y;                                // group of query heads
+  const int kvh = (hy * gs) / (a.heads / a.kv_heads);
+  const int* bt = a.block_tables + static_cast<long long>(s) * a.max_blocks;
+  const long long crow = static_cast<long long>(a.kv_heads) * (D + Dv);
+  const bf16* cache = static_cast<const bf16*>(a.cache);
+  const long long koff = static_cast<long long>(kvh) * D, voff = static_cast<long long>(a.kv_heads) * D + static_cast<long long>(kvh) * Dv;
+  // queries -> bf16 rows (row r: token r / gs, head hy * gs + r % gs)
+  for (int e = tid; e < kTileRows * (D / 2); e += 128) {
+    const int r = e / (D / 2), c = (e - r * (D / 2)) * 2;
+    const int tq = r / gs, hh = r - tq * gs;
+    float2 v = make_float2(0.f, 0.f);
+    if (tq < ntq) v = *reinterpret_cast<const float2*>(a.qn + (static_cast<long long>(tok0 + tq) * a.heads + hy * gs + hh) * D + c);
+    *reinterpret_cast<uint32_t*>(Qs + r * LDK + c) = pack_bf16(v.x, v.y);
+  }
+  const int lo0 = max(0, p0 - a.window + 1);
+  const int nsink = min(a.keep_first, lo0);
+  const int nst = (nsink + kTileKeys - 1) / kTileKeys;
+  const int nwt = (p1 - lo0 + 1 + kTileKeys - 1) / kTileKeys;
+  const int ntiles = nst + nwt;
+  const int kchunks = D / 8, vchunks = Dv / 8;
+  auto tile_range = [&](int i, int* j0, int* cnt) {
+    if (i < nst) { *j0 = i * kTileKeys; *cnt = min(kTileKeys, nsink - *j0); }
+    else { *j0 = lo0 + (i - nst) * kTileKeys; *cnt = min(kTileKeys, p1 + 1 - *j0); }
+  };
+  auto load_tile = [&](int i) {
+    int j0, cnt;
+    tile_range(i, &j0, &cnt);
+    bf16* kd = Ks + (i & 1) * kTileKeys * LDK;
+    bf16* vd = Vs + (i & 1) * kTileKeys * LDV;
+    for (int e = tid; e < kTileKeys * (kchunks + vchunks); e += 128) {
+      const int r = e / (kchunks + vchunks), c = e - r * (kchunks + vchunks);
+      const int j = j0 + min(r, cnt - 1);      // rows past the range repeat its last key: finite values under a zero weight
+      const long long row = static_cast<long long>(bt[j / a.page]) * a.page + j % a.page;
+      if (c < kchunks) cp_async16(smem_u32(kd + r * LDK + c * 8), cache + row * crow + koff + c * 8);
+      else cp_async16(smem_u32(vd + r * LDV + (c - kchunks) * 8), cache + row * crow + voff + (c - kchunks) * 8);
+    }
+  };
+  float m[2] = {kMasked, kMasked}, l[2] = {0.f, 0.f};
+  float o[NV][4];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  const int nv = Dv / 8;
+  // this thread's two rows
+  int prow[2];
+  bool rowok[2];
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    const int r = 16 * wrp + g + 8 * hf, tq = r / gs;
+    prow[hf] = p0 + tq;
+    rowok[hf] = tq < ntq;
+  }
+  load_tile(0);
+  cp_async_commit();
+  for (int i = 0; i < ntiles; ++i) {
+    if (i + 1 < ntiles) { load_tile(i + 1); cp_async_commit(); cp_async_wait<1>(); }
+    else cp_async_wait<0>();
+    __syncthreads();
+    int j0, cnt;
+    tile_range(i, &j0, &cnt);
+    const bf16* kt = Ks + (i & 1) * kTileKeys * LDK;
+    const bf16* vt = Vs + (i & 1) * kTileKeys * LDV;
+    float sc[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
+    for (int ks = 0; ks < D; ks += 16) {
+      uint32_t af[4];
+      ldsm_x4(af, smem_u32(Qs + (16 * wrp + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + ks + (lane >> 4) * 8));
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb) {
+        uint32_t bfr[4];
+        ldsm_x4(bfr, smem_u32(kt + (16 * nb + (lane & 7) + (lane >> 4) * 8) * LDK + ks + ((lane >> 3) & 1) * 8));
+        mma_bf16(sc[2 * nb], af, bfr[0], bfr[1]);
+        mma_bf16(sc[2 * nb + 1], af, bfr[2], bfr[3]);
+      }
+    }
+    // mask, scale, running maximum
+    float mx[2] = {kMasked, kMasked};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int hf = e >> 1, col = nt * 8 + 2 * t4 + (e & 1), j = j0 + col, p = prow[hf];
+        const bool vis = rowok[hf] && col < cnt && j <= p && (p - j < a.window || j < a.keep_first);
+        const float v = vis ? sc[nt][e] * a.scale : kMasked;
+        sc[nt][e] = v;
+        mx[hf] = fmaxf(mx[hf], v);
+      }
+    float corr[2];
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 1));
+      mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 2));
+      const float mn = fmaxf(m[hf], mx[hf]);
+      corr[hf] = expf(m[hf] - mn);       // 1 while the row has seen nothing (both at the sentinel)
+      m[hf] = mn;
+      l[hf] *= corr[hf];
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int hf = e >> 1;
+        const float pv = sc[nt][e] <= kMasked ? 0.f : expf(sc[nt][e] - m[hf]);
+        sc[nt][e] = pv;
+        l[hf] += pv;
+      }
+#pragma unroll
+    for (int i2 = 0; i2 < NV; ++i2) { o[i2][0] *= corr[0]; o[i2][1] *= corr[0]; o[i2][2] *= corr[1]; o[i2][3] *= corr[1]; }
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      uint32_t pf[4];
+      pf[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+      pf[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+      pf[2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+      pf[3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+      for (int nb = 0; nb < NV / 2; ++nb) {
+        if (2 * nb < nv) {
+          uint32_t bfr[4];
+          ldsm_x4_trans(bfr, smem_u32(vt + (16 * kk + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + 16 * nb + (lane >> 4) * 8));
+          mma_bf16(o[2 * nb], pf, bfr[0], bfr[1]);
+          mma_bf16(o[2 * nb + 1], pf, bfr[2], bfr[3]);
+        }
+      }
+    }
+    __syncthreads();   // the buffer is free for the tile after next
+  }
+  // finish: row sums over the four lanes of a row, gate, branch scale, one rounding
+  const bf16* gate = static_cast<const bf16*>(a.gate);
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    float ls = l[hf];
+    ls += __shfl_xor_sync(0xffffffffu, ls, 1);
+    ls += __shfl_xor_sync(0xffffffffu, ls, 2);
+    if (!rowok[hf]) continue;
+    const int r = 16 * wrp + g + 8 * hf, tq = r / gs, hh = r - tq * gs;
+    const long long t = tok0 + tq;
+    const int head = hy * gs + hh;
+    const float inv = 1.0f / ls;
+    bf16* y = static_cast<bf16*>(a.y) + t * a.ldy + static_cast<long long>(head) * Dv;
+#pragma unroll
+    for (int i2 = 0; i2 < NV; ++i2) {
+      if (i2 < nv) {
+        const int c = 8 * i2 + 2 * t4;
+        float v0 = o[i2][2 * hf] * inv, v1 = o[i2][2 * hf + 1] * inv;
+        if (gate) {
+          const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(gate + t * a.ldg + static_cast<long long>(head) * Dv + c);
+          v0 *= sigmoidf_(__bfloat162float(gv.x));
+          v1 *= sigmoidf_(__bfloat162float(gv.y));
+        }
+        *reinterpret_cast<uint32_t*>(y + c) = pack_bf16(v0 * a.out_scale, v1 * a.out_scale);
+      }
+    }
   }
 }
 
@@ -250,15 +468,38 @@ int window_attention(const WindowAttnArgs& a, cudaStream_t st) {
   if (a.T <= 0) return 0;
   if (a.heads < 1 || a.kv_heads < 1 || a.heads % a.kv_heads || a.dim < 1 || a.vdim < 1 || a.vdim > 32 * kMaxVR || a.window < 1 || a.keep_first < 0 ||
       a.page < 1) return -1;
-  const size_t es = dtype_bytes(a.t);
+  // Steps that bring portions of prompts take the tensor-core kernel when the head sizes fit its fragments; steps of
+  // single tokens (and every fp32 model) take the general kernel.  B200_WATTN_MMA=0 / 1 forces the choice (A/B knob).
+  const char* fe = getenv("B200_WATTN_MMA");
+  const int force = fe ? atoi(fe) : -1;
+  const bool fits = a.t == DT_BF16 && a.dim % 16 == 0 && a.vdim % 16 == 0 && a.dim <= 128 && a.vdim <= 128 && a.seqs && a.nseq > 0 && a.ldy % 2 == 0 &&
+                    (!a.gate || a.ldg % 2 == 0) && reinterpret_cast<uintptr_t>(a.cache) % 16 == 0;
+  const bool want = force >= 0 ? force != 0 : (a.T >= 32 && a.T >= 8 * a.nseq);
+  if (fits && want) {
+    const int group = a.heads / a.kv_heads;
+    const int gs = kTileRows % group == 0 ? group : 1;
+    const int TQ = kTileRows / gs;
+    const size_t smem = (static_cast<size_t>(3 * kTileRows) * (a.dim + 8) + 2 * static_cast<size_t>(kTileKeys) * (a.vdim + 8)) * sizeof(bf16);
+    dim3 grid(static_cast<unsigned>((a.T + TQ - 1) / TQ + a.nseq), static_cast<unsigned>(a.heads / gs));
+    static std::atomic<unsigned long long> set8{0}, set16{0};
+    if (a.vdim <= 64) {
+      if (!ensure_dynamic_smem(window_attn_mma_kernel<8>, 100 * 1024, &set8)) return -2;
+      window_attn_mma_kernel<8><<<grid, 128, smem, st>>>(a, gs, TQ);
+    } else {
+      if (!ensure_dynamic_smem(window_attn_mma_kernel<16>, 100 * 1024, &set16)) return -2;
+      window_attn_mma_kernel<16><<<grid, 128, smem, st>>>(a, gs, TQ);
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   const int vl = a.t == DT_BF16 ? 8 : 4;
   const bool vec = a.dim % vl == 0 && (static_cast<long long>(a.kv_heads) * (a.dim + a.vdim)) % vl == 0 && reinterpret_cast<uintptr_t>(a.cache) % 16 == 0;
-  (void)es;
-  const size_t smem = (static_cast<size_t>((a.dim + 3) & ~3) + kWarps * (a.vdim + 2)) * sizeof(float);
+  // single-token steps of few sequences: more warps per (token, head) shorten the chain of key chunks a warp walks
+  const int warps = static_cast<long long>(a.T) * a.heads <= 1024 ? kWarpsDecode : kWarps;
+  const size_t smem = (static_cast<size_t>((a.dim + 3) & ~3) + warps * (a.vdim + 2)) * sizeof(float);
   if (smem > 48 * 1024) return -1;
   const unsigned grid = static_cast<unsigned>(static_cast<long long>(a.T) * a.heads);
-  if (a.t == DT_BF16) window_attn_kernel<bf16><<<grid, kWarps * 32, smem, st>>>(a, vec);
-  else window_attn_kernel<float><<<grid, kWarps * 32, smem, st>>>(a, vec);
+  if (a.t == DT_BF16) window_attn_kernel<bf16><<<grid, warps * 32, smem, st>>>(a, vec);
+  else window_attn_kernel<float><<<grid, warps * 32, smem, st>>>(a, vec);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

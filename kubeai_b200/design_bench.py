@@ -1,5 +1,7 @@
-"""Prefill and decode throughput of a registered design beside the built-in Llama model at equal width, depth and
-feed-forward size, on random weights (`bench.py --design nomanex`).  Every number is CUDA-event time of the engine's
+"""Prefill and decode throughput of a registered design beside the closest existing model at equal width, depth, head
+and feed-forward sizes, on random weights (`bench.py --design nomanex`: beside the built-in Llama model;
+`bench.py --design zinavik`: beside Nomanex, whose recurrent scan, windowed attention and routed experts are the like
+kernels).  Every number is CUDA-event time of the engine's
 own step (b200_feed_step: the same packing, page pool, state slots and kernels as a scheduled step), after warm-up
 steps, with a buffer larger than L2 written between timed steps.  Per-kernel times come from a separate pass in which
 each launch is bracketed by events (b200_engine_profile_kernels for the design, b200_engine_profile_range for Llama),
@@ -30,6 +32,18 @@ def nomanex_config(z):
               dict(type="gla", mixer=gl, mlp=dn), dict(type="latent_attention", mixer=lat, mlp=mo)]
     return dict(architecture="Nomanex", vocab=z["vocab"], width=z["width"], residual_mult=0.5, norm=dict(eps=1e-5),
                 embedding=dict(bigram=dict(buckets=65521, mul_prev=127, mul_cur=17)), layers=layers)
+
+
+def zinavik_config(z):
+    H = z["heads"]
+    lf = dict(heads=H, kv_heads=max(1, H // 4), dim=DIM, vdim=VDIM, mask=dict(size=z["window"], keep_first=4),
+              rot=dict(base=10000.0, dims=ROT, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0)), scale=DIM ** -0.5)
+    rt = dict(heads=H, dim=DIM, vdim=VDIM, decay=[1.0 - 2.0 ** -(5.0 + 5.0 * h / max(H - 1, 1)) for h in range(H)])
+    mo = dict(kind="moe", expert=dict(ff=z["eff"], limit=7.0), router=dict(experts=z["experts"], top=z["top"]),
+              shared=dict(ff=z["eff"], limit=7.0))
+    ly = dict(type="parallel", mixer=dict(left=lf, right=rt, left_scale=1.0, right_scale=1.0), mlp=mo)
+    return dict(architecture="Zinavik", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-5), embedding=dict(scale=1.0), streams=2,
+                layers=[ly, ly, ly, ly])
 
 
 def flush_l2(torch, buf):
@@ -63,16 +77,10 @@ def run_engine(e, torch, buf, vocab, batch, prompt, decode_steps, warmup):
     return out, rids
 
 
-def bench_size(name, z, batch, prompt, decode_steps, warmup, peaks):
-    import torch
+def run_design(cfgj, lim, z, batch, prompt, decode_steps, warmup, peaks, torch, buf):
+    """One registered design on random weights: step times, per-kernel times and fractions of the measured peaks."""
     from .engine import Engine, default_config
     hbm, tf, _ = peaks
-    buf = torch.zeros(160 << 20, dtype=torch.int16, device="cuda")   # 320 MB > 126 MB of L2
-    lim = dict(manual_step=1, enable_prefix_caching=0, max_num_seqs=batch, max_batched_tokens=batch * prompt,
-               max_model_len=prompt + warmup + decode_steps + 64, record_steps=4, seed=1)
-    lim["num_kv_blocks"] = batch * ((lim["max_model_len"] + 15) // 16)
-    res = {"size": dict(z, batch=batch, prompt=prompt)}
-    cfgj = nomanex_config(z)
     T = batch * prompt
     with tempfile.TemporaryDirectory() as d:
         with open(os.path.join(d, "config.json"), "w") as f:
@@ -93,25 +101,74 @@ def bench_size(name, z, batch, prompt, decode_steps, warmup, peaks):
             e.profile_kernels(False)
             r["kernels_prefill_us"] = {k: round(v["us"], 1) for k, v in sorted(kp.items())}
             r["kernels_decode_us"] = {k: round(v["us"], 1) for k, v in sorted(kd.items())}
-            # algorithmic work of the two mixers and of the projections (per step, both layers of a kind together)
-            H, E, W = z["heads"], RANK + ROT, z["width"]
-            keys = sum(min(p + 1, z["window"]) for p in range(prompt)) * batch
-            att_flops = 2.0 * 2 * H * keys * (E + RANK)
-            gla_flops = 2.0 * 3 * 2 * T * H * DIM * VDIM
-            n_in = sum(_n_in(ly, W) for ly in cfgj["layers"])
-            k_out = sum(_k_out(ly) for ly in cfgj["layers"])
-            proj_flops = 2.0 * T * W * (n_in + k_out)
-            state_bytes = 2.0 * 2 * batch * H * DIM * VDIM * 4
-            dkeys = batch * min(prompt + 1, z["window"])
-            r["roofline"] = {
-                "latent_attention_prefill_frac_of_bf16_peak": att_flops / (kp["latent_attention"]["us"] * 1e-6) / (tf * 1e12),
-                "gla_scan_prefill_tflops": gla_flops / (kp["gla_scan"]["us"] * 1e-6) / 1e12,
-                "projections_prefill_frac_of_bf16_peak": proj_flops / ((kp["proj_in"]["us"] + kp["proj_out"]["us"]) * 1e-6) / (tf * 1e12),
-                "gla_scan_decode_frac_of_hbm": state_bytes / (kd["gla_scan"]["us"] * 1e-6) / (hbm * 1e9),
-                "latent_attention_decode_frac_of_hbm": 2.0 * dkeys * E * 2 / (kd["latent_attention"]["us"] * 1e-6) / (hbm * 1e9),
-                "projections_decode_frac_of_hbm": 2.0 * W * (n_in + k_out) / ((kd["proj_in"]["us"] + kd["proj_out"]["us"]) * 1e-6) / (hbm * 1e9),
-            }
-        res["nomanex"] = r
+            H, W = z["heads"], z["width"]
+            us = lambda k, name: k[name]["us"] * 1e-6
+            if cfgj["architecture"] == "Nomanex":
+                # algorithmic work of the two mixers and of the projections (per step, both layers of a kind together)
+                E = RANK + ROT
+                keys = sum(min(p + 1, z["window"]) for p in range(prompt)) * batch
+                att_flops = 2.0 * 2 * H * keys * (E + RANK)
+                gla_flops = 2.0 * 3 * 2 * T * H * DIM * VDIM
+                n_in = sum(_n_in(ly, W) for ly in cfgj["layers"])
+                k_out = sum(_k_out(ly) for ly in cfgj["layers"])
+                proj_flops = 2.0 * T * W * (n_in + k_out)
+                state_bytes = 2.0 * 2 * batch * H * DIM * VDIM * 4
+                dkeys = batch * min(prompt + 1, z["window"])
+                nl = len(cfgj["layers"]) + 1
+                r["roofline"] = {
+                    "latent_attention_prefill_frac_of_bf16_peak": att_flops / us(kp, "latent_attention") / (tf * 1e12),
+                    "gla_scan_prefill_tflops": gla_flops / us(kp, "gla_scan") / 1e12,
+                    "projections_prefill_frac_of_bf16_peak": proj_flops / (us(kp, "proj_in") + us(kp, "proj_out")) / (tf * 1e12),
+                    "gla_scan_decode_frac_of_hbm": state_bytes / us(kd, "gla_scan") / (hbm * 1e9),
+                    "latent_attention_decode_frac_of_hbm": 2.0 * dkeys * E * 2 / us(kd, "latent_attention") / (hbm * 1e9),
+                    "projections_decode_frac_of_hbm": 2.0 * W * (n_in + k_out) / (us(kd, "proj_in") + us(kd, "proj_out")) / (hbm * 1e9),
+                    # residual update + norm: reads the fp32 residual and two bf16 sublayer outputs, writes the residual and a bf16 row
+                    "residual_norm_prefill_frac_of_hbm": nl * T * W * (4 + 4 + 2 + 2 + 2) / us(kp, "residual_norm") / (hbm * 1e9),
+                    "moe_experts_prefill_frac_of_bf16_peak": 2.0 * 2 * T * z["top"] * 2 * W * z["eff"] / (us(kp, "moe_up") + us(kp, "moe_down")) / (tf * 1e12),
+                }
+            else:
+                L = len(cfgj["layers"])
+                lf = cfgj["layers"][0]["mixer"]["left"]
+                G, ns = lf["kv_heads"], cfgj["streams"]
+                keys = sum(min(p + 1, z["window"]) + min(lf["mask"]["keep_first"], max(0, p + 1 - z["window"])) for p in range(prompt)) * batch
+                att_flops = 2.0 * L * H * keys * (DIM + VDIM)
+                scan_flops = 2.0 * 3 * L * T * H * DIM * VDIM
+                n_in = L * (H * DIM + G * DIM + G * VDIM + H * VDIM + 2 * H * DIM + 2 * H * VDIM)
+                k_out = L * 2 * H * VDIM
+                proj_flops = 2.0 * T * W * (n_in + k_out)
+                state_bytes = 2.0 * L * batch * H * DIM * VDIM * 4
+                dkeys = batch * (min(prompt + 1, z["window"]) + min(lf["mask"]["keep_first"], max(0, prompt + 1 - z["window"])))
+                calls = 2 * L + 1      # one boundary per sublayer, the last write-back alone (the head's norm touches `batch` rows)
+                r["roofline"] = {
+                    "window_attention_prefill_frac_of_bf16_peak": att_flops / us(kp, "window_attention") / (tf * 1e12),
+                    "lightning_scan_prefill_tflops": scan_flops / us(kp, "lightning_scan") / 1e12,
+                    "projections_prefill_frac_of_bf16_peak": proj_flops / (us(kp, "proj_in") + us(kp, "proj_out")) / (tf * 1e12),
+                    "lightning_scan_decode_frac_of_hbm": state_bytes / us(kd, "lightning_scan") / (hbm * 1e9),
+                    "window_attention_decode_frac_of_hbm": L * dkeys * G * (DIM + VDIM) * 2.0 / us(kd, "window_attention") / (hbm * 1e9),
+                    "projections_decode_frac_of_hbm": 2.0 * W * (n_in + k_out) / (us(kd, "proj_in") + us(kd, "proj_out")) / (hbm * 1e9),
+                    # stream boundary: reads and writes `ns` fp32 streams, reads a bf16 sublayer output, writes a bf16 row
+                    "stream_norm_prefill_frac_of_hbm": calls * T * W * (8.0 * ns + 2 + 2) / us(kp, "stream_norm") / (hbm * 1e9),
+                    "moe_experts_prefill_frac_of_bf16_peak": 2.0 * L * T * z["top"] * 3 * W * z["eff"] / (us(kp, "moe_up") + us(kp, "moe_down")) / (tf * 1e12),
+                }
+    return r
+
+
+def bench_size(design, name, z, batch, prompt, decode_steps, warmup, peaks):
+    import torch
+    from .engine import Engine, default_config
+    hbm, tf, _ = peaks
+    buf = torch.zeros(160 << 20, dtype=torch.int16, device="cuda")   # 320 MB > 126 MB of L2
+    lim = dict(manual_step=1, enable_prefix_caching=0, max_num_seqs=batch, max_batched_tokens=batch * prompt,
+               max_model_len=prompt + warmup + decode_steps + 64, record_steps=4, seed=1)
+    lim["num_kv_blocks"] = batch * ((lim["max_model_len"] + 15) // 16)
+    res = {"size": dict(z, batch=batch, prompt=prompt)}
+    T = batch * prompt
+    if design == "zinavik":
+        res["zinavik"] = run_design(zinavik_config(z), lim, z, batch, prompt, decode_steps, warmup, peaks, torch, buf)
+        res["nomanex"] = run_design(nomanex_config(z), lim, z, batch, prompt, decode_steps, warmup, peaks, torch, buf)
+        del buf
+        return res
+    res["nomanex"] = run_design(nomanex_config(z), lim, z, batch, prompt, decode_steps, warmup, peaks, torch, buf)
     # the closest existing model: Llama at equal width, depth, heads x 128 and feed-forward size
     lcfg = default_config(num_layers=4, hidden=z["width"], q_heads=z["heads"], kv_heads=z["heads"] // 4, intermediate=z["ff"],
                           vocab=z["vocab"], **lim)
@@ -158,11 +215,11 @@ def _k_out(ly):
 
 
 def run(design, peaks, sizes=None, batch=8, prompt=512, decode_steps=8, warmup=3):
-    if design != "nomanex":
-        raise SystemExit("unknown design %r (known: nomanex)" % design)
+    if design not in ("nomanex", "zinavik"):
+        raise SystemExit("unknown design %r (known: nomanex, zinavik)" % design)
     out = {"design": design, "dtype": "bf16", "data": "synthetic (seeded random weights and tokens)", "peaks": dict(hbm_gbs=peaks[0], bf16_tflops=peaks[1], source=peaks[2]),
            "timing": "CUDA events around the engine step, median of the timed steps, %d warm-up steps, 320 MB written between steps" % warmup,
            "sizes": {}}
     for name in sizes or list(SIZES):
-        out["sizes"][name] = bench_size(name, SIZES[name], batch, prompt, decode_steps, warmup, peaks)
+        out["sizes"][name] = bench_size(design, name, SIZES[name], batch, prompt, decode_steps, warmup, peaks)
     return out

@@ -153,6 +153,27 @@ def test_bfloat16_large_step_takes_the_per_expert_path_and_agrees_with_the_group
     assert np.median(rel_err(big, grouped.astype(np.float64))) < 0.03
 
 
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,window,keep", [(4, 1, 16, 16, 100, 0), (2, 2, 32, 48, 70, 9), (6, 2, 64, 32, 33, 20), (8, 4, 128, 128, 150, 3),
+                                                                 (3, 3, 16, 32, 500, 0), (12, 2, 16, 16, 64, 64)])
+def test_bfloat16_tensor_core_attention_equals_the_general_kernel(tmp_path, monkeypatch, heads, kv_heads, dim, vdim, window, keep):
+    """Head sizes that fit the mma fragments take the tensor-core kernel in steps that bring prompt portions: several key
+    tiles per window, kept tokens before the window, groups of 1 to 6 query heads per key head, portions that start in
+    the middle of a tile.  The general kernel on the same bf16 cache must agree far inside bf16's distance to the oracle."""
+    layers = [layer(l=left(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, window=window, keep_first=keep, rot_dims=dim // 2, scale=2.0 / dim ** 0.5),
+                    right_scale=0.3, mlp=None)]
+    cfg, W, d = build(tmp_path, layers, seed=21, q_gain=2.0, width=32)
+    t = toks(230, cfg["vocab"], 22)
+    want = oracle_for(cfg, W).forward(t)
+    out = {}
+    for knob in ("1", "0"):
+        monkeypatch.setenv("B200_WATTN_MMA", knob)
+        with open_engine(d, dtype="bfloat16") as e:
+            out[knob] = (feed_whole(e, t), feed_portions(e, t, [70, 37, 64, 5, 1]))
+    for a, b in zip(out["1"], out["0"]):
+        close16(a, want)
+        assert np.median(rel_err(a, b.astype(np.float64))) < 0.012 and rel_err(a, b.astype(np.float64)).max() < 0.05
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_medium_sizes_on_every_projection_path(tmp_path, dtype):
     layers = [layer(l=left(heads=4, kv_heads=2, dim=16, vdim=24, window=33, keep_first=5), r=right(heads=2, dim=16, vdim=24),
@@ -314,7 +335,7 @@ QTOK, KTOK = 7, 11
 def edge_model(tmp_path, window, keep_first, seed=31):
     """One layer whose left branch copies from KTOK positions whenever a QTOK position can see one (planted pair, sharp
     softmax, mostly unrotated dimensions); the right branch is switched off so that nothing else carries KTOK forward."""
-    l = left(heads=2, kv_heads=1, dim=16, vdim=8, window=window, keep_first=keep_first, rot_dims=2, scaling=None, scale=3.0)
+    l = left(heads=2, kv_heads=1, dim=16, vdim=16, window=window, keep_first=keep_first, rot_dims=2, scaling=None, scale=3.0)
     cfg = make_config([layer(l=l, right_scale=0.0, mlp=None)], width=48, vocab=40)
     W = plant_pair(cfg, random_weights(cfg, seed=seed), QTOK, KTOK)
     return cfg, W, write_model_dir(tmp_path / ("m%d_%d" % (window, keep_first)), cfg, W)
