@@ -173,23 +173,35 @@ __global__ void gla_out_gate_kernel(const float* o, const T* g, int ldg, const f
   }
 }
 
-// The general output stage: one warp per (token, head), or per token when the norm runs over the concatenated heads.
+// The general output stage.  Per-head norm: one warp per (token, head).  Norm over the concatenated heads: one CTA per
+// token, the warps' sums of squares added in warp order.
 template <typename T>
 __global__ void recurrent_out_gate_kernel(OutGateArgs a, long long units) {
-  const long long p = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (p >= units) return;
-  const int lane = threadIdx.x & 31;
-  const int n = a.joint ? a.heads * a.vdim : a.vdim;        // elements normed together
-  const long long t = a.joint ? p : p / a.heads;
-  const int c0 = a.joint ? 0 : static_cast<int>(p - t * a.heads) * a.vdim;   // first column of the unit in the token's row
+  __shared__ float red[8];
+  const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
+  long long t;
+  int c0, n, first, step;
+  if (a.joint) {
+    t = blockIdx.x; c0 = 0; n = a.heads * a.vdim; first = threadIdx.x; step = blockDim.x;
+  } else {
+    const long long p = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + wrp;
+    if (p >= units) return;
+    t = p / a.heads; c0 = static_cast<int>(p - t * a.heads) * a.vdim; n = a.vdim; first = lane; step = 32;
+  }
   const float* op = a.o + t * (static_cast<long long>(a.heads) * a.vdim) + c0;
   const T* g = static_cast<const T*>(a.g) + t * a.ldg + c0;
   T* y = static_cast<T*>(a.y) + t * a.ldy + c0;
   float ss = 0.f;
-  for (int i = lane; i < n; i += 32) ss = fmaf(op[i], op[i], ss);
+  for (int i = first; i < n; i += step) ss = fmaf(op[i], op[i], ss);
   for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+  if (a.joint) {
+    if (lane == 0) red[wrp] = ss;
+    __syncthreads();
+    ss = 0.f;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) ss += red[w];
+  }
   const float inv = 1.0f / sqrtf(ss / static_cast<float>(n) + a.eps);
-  for (int i = lane; i < n; i += 32) {
+  for (int i = first; i < n; i += step) {
     const float gv = ldf(g + i);
     const float sg = 1.0f / (1.0f + expf(-gv));
     const float gate = a.gate_act == GATE_SIGMOID ? sg : gv * sg;
@@ -203,9 +215,10 @@ int recurrent_out_gate(const OutGateArgs& a, cudaStream_t st) {
   const long long units = a.joint ? a.T : static_cast<long long>(a.T) * a.heads;
   if (units <= 0) return 0;
   if (!a.o || !a.g || !a.w || !a.y || a.heads < 1 || a.vdim < 1) return -1;
-  const unsigned grid = static_cast<unsigned>((units + 3) / 4);
-  if (a.t == DT_BF16) recurrent_out_gate_kernel<bf16><<<grid, 128, 0, st>>>(a, units);
-  else recurrent_out_gate_kernel<float><<<grid, 128, 0, st>>>(a, units);
+  const int th = a.joint ? (a.heads * a.vdim >= 1024 ? 256 : 128) : 128;
+  const unsigned grid = static_cast<unsigned>(a.joint ? units : (units + 3) / 4);
+  if (a.t == DT_BF16) recurrent_out_gate_kernel<bf16><<<grid, th, 0, st>>>(a, units);
+  else recurrent_out_gate_kernel<float><<<grid, th, 0, st>>>(a, units);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -110,6 +110,111 @@ __global__ void hyper_step_kernel(HyperArgs a) {
   for (int i = threadIdx.x; i < a.W; i += blockDim.x) stf(h + i, us[i] * inv * a.norm_w[i]);
 }
 
+// The same boundary for W % 4 == 0: a thread owns four neighbouring columns per round (16-byte loads and stores of the
+// streams, 8-byte ones of bf16 rows).
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const bf16* p) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(bf16* p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
+template <typename TY, typename TH>
+__global__ void __launch_bounds__(256) hyper_step_vec_kernel(HyperArgs a) {
+  extern __shared__ __align__(16) float us[];
+  __shared__ float red[32];
+  __shared__ float coef[kMaxStreams * kMaxStreams + 2 * kMaxStreams];
+  const int r = blockIdx.x, n = a.streams;
+  const long long t = a.row_index ? a.row_index[r] : r;
+  float* mixs = coef;
+  float* outs = coef + kMaxStreams * kMaxStreams;
+  float* ins = outs + kMaxStreams;
+  if (threadIdx.x < n * n) mixs[threadIdx.x] = a.mix ? a.mix[threadIdx.x] : (threadIdx.x / n == threadIdx.x % n ? 1.f : 0.f);
+  if (threadIdx.x < n) {
+    outs[threadIdx.x] = a.out ? a.out[threadIdx.x] : 1.f;
+    ins[threadIdx.x] = a.in ? a.in[threadIdx.x] : 1.f;
+  }
+  __syncthreads();
+  const TY* y = static_cast<const TY*>(a.y);
+  const bool plain = !a.mix;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < a.W; i += blockDim.x * 4) {
+    float xs[kMaxStreams][4];
+#pragma unroll
+    for (int s = 0; s < kMaxStreams; ++s)
+      if (s < n) { const float4 v = ld4(a.x + s * a.stream_stride + t * a.W + i); xs[s][0] = v.x; xs[s][1] = v.y; xs[s][2] = v.z; xs[s][3] = v.w; }
+    if (y) {
+      const float4 y4 = ld4(y + t * a.W + i);
+      const float yv[4] = {y4.x, y4.y, y4.z, y4.w};
+      float nx[kMaxStreams][4];
+#pragma unroll
+      for (int j = 0; j < kMaxStreams; ++j) {
+        if (j < n) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float acc;
+            if (plain) acc = xs[j][c];
+            else {
+              acc = 0.f;
+#pragma unroll
+              for (int s = 0; s < kMaxStreams; ++s)
+                if (s < n) acc = fmaf(mixs[s * n + j], xs[s][c], acc);
+            }
+            nx[j][c] = fmaf(outs[j], yv[c], acc);
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kMaxStreams; ++j)
+        if (j < n) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) xs[j][c] = nx[j][c];
+          st4(a.x + j * a.stream_stride + t * a.W + i, make_float4(nx[j][0], nx[j][1], nx[j][2], nx[j][3]));
+        }
+    }
+    if (a.h) {
+      float u[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float v = 0.f;
+        if (a.in) {
+#pragma unroll
+          for (int s = 0; s < kMaxStreams; ++s)
+            if (s < n) v = fmaf(ins[s], xs[s][c], v);
+        } else {
+#pragma unroll
+          for (int s = 0; s < kMaxStreams; ++s)
+            if (s < n) v += xs[s][c];
+        }
+        u[c] = v;
+        ss = fmaf(v, v, ss);
+      }
+      st4(us + i, make_float4(u[0], u[1], u[2], u[3]));
+    }
+  }
+  if (!a.h) return;
+  TH* h = static_cast<TH*>(a.h) + static_cast<long long>(r) * a.W;
+  if (!a.norm_w) {
+    for (int i = threadIdx.x * 4; i < a.W; i += blockDim.x * 4) st4(h + i, ld4(us + i));
+    return;
+  }
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
+  if (lane == 0) red[wrp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
+  const float inv = 1.0f / sqrtf(tot / static_cast<float>(a.W) + a.eps);
+  for (int i = threadIdx.x * 4; i < a.W; i += blockDim.x * 4) {
+    const float4 u = ld4(us + i), w = ld4(a.norm_w + i);
+    st4(h + i, make_float4(u.x * inv * w.x, u.y * inv * w.y, u.z * inv * w.z, u.w * inv * w.w));
+  }
+}
+
 inline int threads_for(int W) { return W >= 2048 ? 256 : (W >= 256 ? 128 : 64); }
 
 }  // namespace
@@ -129,8 +234,11 @@ int hyper_step(const HyperArgs& a, cudaStream_t st) {
   if (a.y && a.row_index) return -1;   // an update of chosen rows only would leave the streams inconsistent
   const size_t smem = a.h ? static_cast<size_t>(a.W) * sizeof(float) : 0;
   if (smem > 48 * 1024) return -1;
-  const int th = threads_for(a.W);
-#define HS(TY, TH) hyper_step_kernel<TY, TH><<<a.rows, th, smem, st>>>(a)
+  // four columns per thread where every row start is 16-byte aligned
+  const bool vec = a.W % 4 == 0 && a.stream_stride % 4 == 0 && reinterpret_cast<uintptr_t>(a.x) % 16 == 0 && reinterpret_cast<uintptr_t>(a.y) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(a.h) % 16 == 0 && reinterpret_cast<uintptr_t>(a.norm_w) % 16 == 0;
+  const int th = vec ? (a.W >= 1024 ? 256 : (a.W >= 512 ? 128 : 64)) : threads_for(a.W);
+#define HS(TY, TH) do { if (vec) hyper_step_vec_kernel<TY, TH><<<a.rows, th, smem, st>>>(a); else hyper_step_kernel<TY, TH><<<a.rows, th, smem, st>>>(a); } while (0)
   const bool y16 = a.y && a.ty == DT_BF16, h16 = a.h && a.th == DT_BF16;
   if (y16 && h16) HS(bf16, bf16);
   else if (y16) HS(bf16, float);

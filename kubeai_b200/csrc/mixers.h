@@ -198,8 +198,9 @@ int hyper_step(const HyperArgs& a, cudaStream_t st);
 // chosen (ties: lower index) and used unchanged as weights.  topk_ids / topk_w: [T, top].
 // score_fn: MOE_SOFTMAX as above, MOE_SIGMOID scores every expert by sigmoid(z) on its own (no normalisation over E).
 enum MoeScore { MOE_SOFTMAX = 0, MOE_SIGMOID = 1 };
+// ld: leading dimension of scores (0: E); columns past E are left alone (a design may keep other fp32 outputs there).
 int moe_route(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, cudaStream_t st,
-              int score_fn = MOE_SOFTMAX);
+              int score_fn = MOE_SOFTMAX, int ld = 0);
 // Sort the T * top (token, choice) pairs by expert into 64-row tiles: sorted_rows[cap] = token of each sorted row or -1,
 // tile_group[cap / 64] = expert of each tile or -1, pair_pos[T * top] = sorted row of each pair.  cap >= T*top + E*64.
 // expert_rows (optional): [E][2] = {first sorted row, rows} of every expert.
@@ -211,8 +212,8 @@ int moe_align(const int* topk_ids, int T, int top, int E, int* sorted_rows, int*
 int moe_combine(const void* y, DType ty, const int* pair_pos, const float* topk_w, void* out, DType t, int T, int top, int W, cudaStream_t st);
 // out[t] = sum_k w[t, k] * y[pair_pos[t * top + k]] + sigmoid(add_gate[t * ld_gate]) * add[t]: the routed experts plus a
 // shared expert behind a per-token gate.  topk_w may be null (every weight 1: the weight was applied to the expert's
-// input); add ([T, W]) and add_gate are of type t, add_gate may be null (gate 1), add may be null (no shared expert).
-int moe_combine_add(const void* y, DType ty, const int* pair_pos, const float* topk_w, const void* add, const void* add_gate, int ld_gate,
+// input); add ([T, W]) is of type t and may be null (no shared expert); add_gate is fp32 and may be null (gate 1).
+int moe_combine_add(const void* y, DType ty, const int* pair_pos, const float* topk_w, const void* add, const float* add_gate, int ld_gate,
                     void* out, DType t, int T, int top, int W, cudaStream_t st);
 // bf16 helpers of the per-expert tensor-core path: x rows in sorted order (negative source row -> zeros; with row_scale the
 // row is multiplied by row_scale[r] in fp32 and rounded once), max(p, 0)^2 in place

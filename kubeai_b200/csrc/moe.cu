@@ -17,11 +17,11 @@ namespace {
 typedef __nv_bfloat16 bf16;
 
 // one warp per token; scores row in global memory is the scratch (chosen entries are overwritten with -1)
-__global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, int score_fn) {
+__global__ void moe_route_kernel(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, int score_fn, int ld) {
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
   const int lane = threadIdx.x & 31;
-  float* s = scores + static_cast<long long>(t) * E;
+  float* s = scores + static_cast<long long>(t) * ld;
   if (score_fn == MOE_SIGMOID) {
     for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
   } else {
@@ -116,10 +116,10 @@ __device__ __forceinline__ float ldy(const bf16* p) { return __bfloat162float(*p
 
 template <typename T, typename TYIN>
 __global__ void moe_combine_kernel(const TYIN* y, const int* pair_pos, const float* topk_w, T* out, int top, int W, const T* add = nullptr,
-                                   const T* add_gate = nullptr, int ld_gate = 0) {
+                                   const float* add_gate = nullptr, int ld_gate = 0) {
   const long long t = blockIdx.x;
   float gate = 1.f;
-  if (add && add_gate) gate = 1.0f / (1.0f + expf(-ldy(add_gate + t * ld_gate)));
+  if (add && add_gate) gate = 1.0f / (1.0f + expf(-add_gate[t * ld_gate]));
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < top; ++k) {
@@ -134,10 +134,10 @@ __global__ void moe_combine_kernel(const TYIN* y, const int* pair_pos, const flo
 
 }  // namespace
 
-int moe_route(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, cudaStream_t st, int score_fn) {
+int moe_route(float* scores, int* topk_ids, float* topk_w, int T, int E, int groups, int keep, int top, cudaStream_t st, int score_fn, int ld) {
   if (T <= 0) return 0;
   if (E < 1 || groups < 1 || groups > 64 || E % groups || keep < 1 || keep > groups || top < 1 || top > keep * (E / groups)) return -1;
-  moe_route_kernel<<<(T + 3) / 4, 128, 0, st>>>(scores, topk_ids, topk_w, T, E, groups, keep, top, score_fn);
+  moe_route_kernel<<<(T + 3) / 4, 128, 0, st>>>(scores, topk_ids, topk_w, T, E, groups, keep, top, score_fn, ld > 0 ? ld : E);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -162,20 +162,20 @@ int moe_combine(const void* y, DType ty, const int* pair_pos, const float* topk_
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-int moe_combine_add(const void* y, DType ty, const int* pair_pos, const float* topk_w, const void* add, const void* add_gate, int ld_gate,
+int moe_combine_add(const void* y, DType ty, const int* pair_pos, const float* topk_w, const void* add, const float* add_gate, int ld_gate,
                     void* out, DType t, int T, int top, int W, cudaStream_t st) {
   if (T <= 0) return 0;
   if (!y || !pair_pos || !out || top < 1 || (ty == DT_BF16 && t != DT_BF16)) return -1;
   const int th = W >= 1024 ? 256 : 128;
   if (ty == DT_BF16)
     moe_combine_kernel<bf16, bf16><<<T, th, 0, st>>>(static_cast<const bf16*>(y), pair_pos, topk_w, static_cast<bf16*>(out), top, W,
-                                                       static_cast<const bf16*>(add), static_cast<const bf16*>(add_gate), ld_gate);
+                                                       static_cast<const bf16*>(add), add_gate, ld_gate);
   else if (t == DT_BF16)
     moe_combine_kernel<bf16, float><<<T, th, 0, st>>>(static_cast<const float*>(y), pair_pos, topk_w, static_cast<bf16*>(out), top, W,
-                                                        static_cast<const bf16*>(add), static_cast<const bf16*>(add_gate), ld_gate);
+                                                        static_cast<const bf16*>(add), add_gate, ld_gate);
   else
     moe_combine_kernel<float, float><<<T, th, 0, st>>>(static_cast<const float*>(y), pair_pos, topk_w, static_cast<float*>(out), top, W,
-                                                         static_cast<const float*>(add), static_cast<const float*>(add_gate), ld_gate);
+                                                         static_cast<const float*>(add), add_gate, ld_gate);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -9,11 +9,11 @@
 // when they are written, and never again.
 //
 // Kernels: `qk_prep_kernel` (one CTA per token: rotate, normalise, write the cache row), `window_attn_kernel` (any head
-// size, bf16 or fp32 cache: one CTA per (token, head), four warps share the token's keys in 32-key chunks, a lane owns
+// size, bf16 or fp32 cache: one CTA per (token, head), its warps share the token's keys in 32-key chunks, a lane owns
 // one key for the scores and a slice of the value columns for the output, online softmax in fp32, the warps' partial
 // results meet in shared memory in a fixed order; the sigmoid output gate and the branch scale are applied before the
 // single rounding to the storage type), and `window_attn_mma_kernel` (bf16, head sizes that fit the mma.sync fragments:
-// 64 query rows of one sequence, the heads of one key/value group together, against 64-key tiles on the tensor cores).
+// 128 query rows of one sequence, the heads of one key/value group together, against 64-key tiles on the tensor cores).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <float.h>
@@ -217,13 +217,14 @@ __global__ void __launch_bounds__(kWarpsDecode * 32) window_attn_kernel(WindowAt
 }
 
 // ---------------------------------------------------------------------------------------------- attention on the tensor cores
-// bf16 cache, dim % 16 == 0, vdim % 16 == 0, both <= 128.  A CTA of four warps owns 64 query rows of one sequence: TQ = 64 / gs
-// consecutive tokens times the gs query heads that share one key/value head (gs = heads / kv_heads when that divides 64,
+// bf16 cache, dim % 16 == 0, vdim % 16 == 0, both <= 128.  A CTA of eight warps owns 128 query rows of one sequence: TQ = 128 / gs
+// consecutive tokens times the gs query heads that share one key/value head (gs = heads / kv_heads when that divides 128,
 // else 1 and every query head is its own group), so one key/value tile in shared memory serves the whole group.  Keys
 // come in tiles of 64 from the pages by cp.async, two buffers; first the kept first tokens that lie before the tile's
 // lowest window, then the window itself.  S = Q K^T and O += P V are mma.sync m16n8k16 products with fp32 accumulators;
 // the mask (j <= p, p - j < window or j < keep_first, per row), the scale and the online softmax work on the score
-// fragments in registers, a row's four lanes share its maximum by shuffles.  P is rounded to bf16 for the second product.
+// fragments in registers (fp32; the exponentials are the fast fp32 intrinsic, as bf16 serving allows), a row's four lanes share
+// its maximum by shuffles.  P is rounded to bf16 for the second product.
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void ldsm_x4(uint32_t* r, uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -247,14 +248,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-constexpr int kTileRows = 64, kTileKeys = 64;
+constexpr int kTileRows = 128, kTileKeys = 64, kMmaThreads = 2 * kTileRows, kMmaCtasPerSm = 1;
 constexpr float kMasked = -1e30f;
 
 template <int NV>   // value n-tiles of 8 columns held per thread: vdim <= 8 * NV
-__global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnArgs a, int gs, int TQ) {
+__global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_kernel(WindowAttnArgs a, int gs, int TQ, int page_shift) {
   extern __shared__ __align__(16) unsigned char smraw[];
+  __shared__ long long rowoff[2][kTileKeys];                // cache row (in elements) of every key of a tile, looked up once
   const int D = a.dim, Dv = a.vdim, LDK = D + 8, LDV = Dv + 8;
-  bf16* Qs = reinterpret_cast<bf16*>(smraw);                 // [64][LDK]
+  bf16* Qs = reinterpret_cast<bf16*>(smraw);                 // [128][LDK]
   bf16* Ks = Qs + kTileRows * LDK;                           // [2][64][LDK]
   bf16* Vs = Ks + 2 * kTileKeys * LDK;                       // [2][64][LDV]
   const int tid = threadIdx.x, lane = tid & 31, wrp = tid >> 5, g = lane >> 2, t4 = lane & 3;
@@ -275,35 +277,50 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnArgs a, 
   const long long crow = static_cast<long long>(a.kv_heads) * (D + Dv);
   const bf16* cache = static_cast<const bf16*>(a.cache);
   const long long koff = static_cast<long long>(kvh) * D, voff = static_cast<long long>(a.kv_heads) * D + static_cast<long long>(kvh) * Dv;
-  // queries -> bf16 rows (row r: token r / gs, head hy * gs + r % gs)
-  for (int e = tid; e < kTileRows * (D / 2); e += 128) {
-    const int r = e / (D / 2), c = (e - r * (D / 2)) * 2;
+  // queries -> bf16 rows (row r: token r / gs, head hy * gs + r % gs); a warp takes rows wrp, wrp + 8, ...
+  for (int r = wrp; r < kTileRows; r += kMmaThreads / 32) {
     const int tq = r / gs, hh = r - tq * gs;
-    float2 v = make_float2(0.f, 0.f);
-    if (tq < ntq) v = *reinterpret_cast<const float2*>(a.qn + (static_cast<long long>(tok0 + tq) * a.heads + hy * gs + hh) * D + c);
-    *reinterpret_cast<uint32_t*>(Qs + r * LDK + c) = pack_bf16(v.x, v.y);
+    const float* src = a.qn + (static_cast<long long>(tok0 + tq) * a.heads + hy * gs + hh) * D;
+    for (int c = 2 * lane; c < D; c += 64) {
+      float2 v = make_float2(0.f, 0.f);
+      if (tq < ntq) v = *reinterpret_cast<const float2*>(src + c);
+      *reinterpret_cast<uint32_t*>(Qs + r * LDK + c) = pack_bf16(v.x, v.y);
+    }
   }
   const int lo0 = max(0, p0 - a.window + 1);
   const int nsink = min(a.keep_first, lo0);
   const int nst = (nsink + kTileKeys - 1) / kTileKeys;
   const int nwt = (p1 - lo0 + 1 + kTileKeys - 1) / kTileKeys;
   const int ntiles = nst + nwt;
-  const int kchunks = D / 8, vchunks = Dv / 8;
+  const int kchunks = D / 8, chunks = kchunks + Dv / 8;      // 16-byte pieces of a key row and of a key + value row
   auto tile_range = [&](int i, int* j0, int* cnt) {
     if (i < nst) { *j0 = i * kTileKeys; *cnt = min(kTileKeys, nsink - *j0); }
     else { *j0 = lo0 + (i - nst) * kTileKeys; *cnt = min(kTileKeys, p1 + 1 - *j0); }
   };
+  auto lookup_rows = [&](int i) {     // threads 0..63: the cache row of tile i's keys
+    if (tid < kTileKeys && i < ntiles) {
+      int j0, cnt;
+      tile_range(i, &j0, &cnt);
+      const int j = j0 + min(tid, cnt - 1);    // rows past the range repeat its last key: finite values under a zero weight
+      const long long slot = page_shift >= 0 ? (static_cast<long long>(bt[j >> page_shift]) << page_shift) + (j & ((1 << page_shift) - 1))
+                                             : static_cast<long long>(bt[j / a.page]) * a.page + j % a.page;
+      rowoff[i & 1][tid] = slot * crow;
+    }
+  };
+  // the (row, piece) this thread copies first and its step from one of its pieces to the next: no division per tile
+  const int r_first = tid / chunks, c_first = tid - r_first * chunks;
+  const int r_step = kMmaThreads / chunks, c_step = kMmaThreads - r_step * chunks;
   auto load_tile = [&](int i) {
-    int j0, cnt;
-    tile_range(i, &j0, &cnt);
     bf16* kd = Ks + (i & 1) * kTileKeys * LDK;
     bf16* vd = Vs + (i & 1) * kTileKeys * LDV;
-    for (int e = tid; e < kTileKeys * (kchunks + vchunks); e += 128) {
-      const int r = e / (kchunks + vchunks), c = e - r * (kchunks + vchunks);
-      const int j = j0 + min(r, cnt - 1);      // rows past the range repeat its last key: finite values under a zero weight
-      const long long row = static_cast<long long>(bt[j / a.page]) * a.page + j % a.page;
-      if (c < kchunks) cp_async16(smem_u32(kd + r * LDK + c * 8), cache + row * crow + koff + c * 8);
-      else cp_async16(smem_u32(vd + r * LDV + (c - kchunks) * 8), cache + row * crow + voff + (c - kchunks) * 8);
+    const long long* ro = rowoff[i & 1];
+    int r = r_first, c = c_first;
+    while (r < kTileKeys) {
+      const bf16* src = cache + ro[r];
+      if (c < kchunks) cp_async16(smem_u32(kd + r * LDK + c * 8), src + koff + c * 8);
+      else cp_async16(smem_u32(vd + r * LDV + (c - kchunks) * 8), src + voff + (c - kchunks) * 8);
+      r += r_step; c += c_step;
+      if (c >= chunks) { c -= chunks; ++r; }
     }
   };
   float m[2] = {kMasked, kMasked}, l[2] = {0.f, 0.f};
@@ -320,12 +337,20 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnArgs a, 
     prow[hf] = p0 + tq;
     rowok[hf] = tq < ntq;
   }
+  lookup_rows(0);
+  __syncthreads();
+  // the positions of the warp's 16 rows, for the whole-tile test
+  const int warp_pmin = p0 + (16 * wrp) / gs, warp_pmax = p0 + (16 * wrp + 15) / gs;
+  const bool warp_ok = (16 * wrp + 15) / gs < ntq;
   load_tile(0);
   cp_async_commit();
+  lookup_rows(1);
+  __syncthreads();
   for (int i = 0; i < ntiles; ++i) {
     if (i + 1 < ntiles) { load_tile(i + 1); cp_async_commit(); cp_async_wait<1>(); }
     else cp_async_wait<0>();
     __syncthreads();
+    lookup_rows(i + 2);      // its buffer held tile i's rows, which were consumed when tile i was issued
     int j0, cnt;
     tile_range(i, &j0, &cnt);
     const bf16* kt = Ks + (i & 1) * kTileKeys * LDK;
@@ -344,25 +369,38 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnArgs a, 
         mma_bf16(sc[2 * nb + 1], af, bfr[2], bfr[3]);
       }
     }
-    // mask, scale, running maximum
+    // mask, scale, running maximum.  A tile that every row of the warp sees whole (all keys at or before the warp's
+    // first position and inside its last row's window) needs no per-element test.
     float mx[2] = {kMasked, kMasked};
+    const bool whole = cnt == kTileKeys && warp_ok && j0 + kTileKeys - 1 <= warp_pmin && (warp_pmax - j0 < a.window || j0 + kTileKeys <= a.keep_first);
+    if (whole) {
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
+      for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int hf = e >> 1, col = nt * 8 + 2 * t4 + (e & 1), j = j0 + col, p = prow[hf];
-        const bool vis = rowok[hf] && col < cnt && j <= p && (p - j < a.window || j < a.keep_first);
-        const float v = vis ? sc[nt][e] * a.scale : kMasked;
-        sc[nt][e] = v;
-        mx[hf] = fmaxf(mx[hf], v);
-      }
+        for (int e = 0; e < 4; ++e) {
+          const float v = sc[nt][e] * a.scale;
+          sc[nt][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int hf = e >> 1, col = nt * 8 + 2 * t4 + (e & 1), j = j0 + col, p = prow[hf];
+          const bool vis = rowok[hf] && col < cnt && j <= p && (p - j < a.window || j < a.keep_first);
+          const float v = vis ? sc[nt][e] * a.scale : kMasked;
+          sc[nt][e] = v;
+          mx[hf] = fmaxf(mx[hf], v);
+        }
+    }
     float corr[2];
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
       mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 1));
       mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 2));
       const float mn = fmaxf(m[hf], mx[hf]);
-      corr[hf] = expf(m[hf] - mn);       // 1 while the row has seen nothing (both at the sentinel)
+      corr[hf] = __expf(m[hf] - mn);     // 1 while the row has seen nothing (both at the sentinel)
       m[hf] = mn;
       l[hf] *= corr[hf];
     }
@@ -371,7 +409,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnArgs a, 
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int hf = e >> 1;
-        const float pv = sc[nt][e] <= kMasked ? 0.f : expf(sc[nt][e] - m[hf]);
+        const float pv = sc[nt][e] <= kMasked ? 0.f : __expf(sc[nt][e] - m[hf]);
         sc[nt][e] = pv;
         l[hf] += pv;
       }
@@ -479,15 +517,17 @@ int window_attention(const WindowAttnArgs& a, cudaStream_t st) {
     const int group = a.heads / a.kv_heads;
     const int gs = kTileRows % group == 0 ? group : 1;
     const int TQ = kTileRows / gs;
-    const size_t smem = (static_cast<size_t>(3 * kTileRows) * (a.dim + 8) + 2 * static_cast<size_t>(kTileKeys) * (a.vdim + 8)) * sizeof(bf16);
+    int page_shift = -1;
+    for (int b = 0; b < 31; ++b) if ((1 << b) == a.page) page_shift = b;
+    const size_t smem = (static_cast<size_t>(kTileRows + 2 * kTileKeys) * (a.dim + 8) + 2 * static_cast<size_t>(kTileKeys) * (a.vdim + 8)) * sizeof(bf16);
     dim3 grid(static_cast<unsigned>((a.T + TQ - 1) / TQ + a.nseq), static_cast<unsigned>(a.heads / gs));
     static std::atomic<unsigned long long> set8{0}, set16{0};
     if (a.vdim <= 64) {
-      if (!ensure_dynamic_smem(window_attn_mma_kernel<8>, 100 * 1024, &set8)) return -2;
-      window_attn_mma_kernel<8><<<grid, 128, smem, st>>>(a, gs, TQ);
+      if (!ensure_dynamic_smem(window_attn_mma_kernel<8>, 112 * 1024, &set8)) return -2;
+      window_attn_mma_kernel<8><<<grid, kMmaThreads, smem, st>>>(a, gs, TQ, page_shift);
     } else {
-      if (!ensure_dynamic_smem(window_attn_mma_kernel<16>, 100 * 1024, &set16)) return -2;
-      window_attn_mma_kernel<16><<<grid, 128, smem, st>>>(a, gs, TQ);
+      if (!ensure_dynamic_smem(window_attn_mma_kernel<16>, 112 * 1024, &set16)) return -2;
+      window_attn_mma_kernel<16><<<grid, kMmaThreads, smem, st>>>(a, gs, TQ, page_shift);
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
   }

@@ -75,10 +75,10 @@ struct LayerWeights {
   float *norm1 = nullptr, *norm2 = nullptr, *r_norm = nullptr, *decay = nullptr;
   float2* rope = nullptr;  // [max_model_len][rot_dims / 2]
   Hyper hc1, hc2;
-  void* router = nullptr;  // [experts, width]
+  void* router = nullptr;  // [experts (+ 1), width]: the router rows, then the shared expert's gate row (its logit comes out in fp32 too)
   void* e_gu = nullptr;    // [experts][2 ff][width]  gate rows, then up rows
   void* e_down = nullptr;  // [experts][width][ff]
-  void* sh_in = nullptr;   // [n_sh, width]: gate [sff] | up [sff] | the shared expert's gate row
+  void* sh_in = nullptr;   // [n_sh, width]: gate [sff] | up [sff]
   void* sh_down = nullptr; // [width, sff]
   GemmPlan p_in, p_out, p_shin, p_shdown;
   std::vector<GemmPlan> p_egu, p_edown;
@@ -302,7 +302,7 @@ class Zinavik : public Model {
     s.hv_l = s.l.heads * s.l.vdim;
     s.hv_r = s.r.heads * s.r.vdim;
     s.k_out = s.hv_l + s.hv_r;
-    s.n_sh = s.shared ? up8(2 * s.sff + 1) : 0;
+    s.n_sh = s.shared ? up8(2 * s.sff) : 0;
   }
 
   template <typename P>
@@ -328,7 +328,7 @@ class Zinavik : public Model {
       max_hvr = std::max(max_hvr, s.hv_r);
       if (s.mlp) {
         any_moe = true;
-        max_e = std::max(max_e, s.experts); max_top = std::max(max_top, s.top); max_ff = std::max(max_ff, s.ff);
+        max_e = std::max(max_e, s.experts + 1); max_top = std::max(max_top, s.top); max_ff = std::max(max_ff, s.ff);
         if (s.shared) { any_shared = true; max_nsh = std::max(max_nsh, s.n_sh); max_sff = std::max(max_sff, s.sff); }
       }
     }
@@ -353,7 +353,7 @@ class Zinavik : public Model {
       }
       if (hyper) rc |= vec(&w.hc1.in, ns) | vec(&w.hc1.out, ns) | vec(&w.hc1.mix, static_cast<size_t>(ns) * ns);
       if (s.mlp) {
-        rc |= vec(&w.norm2, W) | mat(&w.router, s.experts, W) | mat(&w.e_gu, static_cast<size_t>(s.experts) * 2 * s.ff, W) |
+        rc |= vec(&w.norm2, W) | mat(&w.router, s.experts + (s.shared ? 1 : 0), W) | mat(&w.e_gu, static_cast<size_t>(s.experts) * 2 * s.ff, W) |
               mat(&w.e_down, static_cast<size_t>(s.experts) * W, s.ff);
         if (hyper) rc |= vec(&w.hc2.in, ns) | vec(&w.hc2.out, ns) | vec(&w.hc2.mix, static_cast<size_t>(ns) * ns);
         if (s.shared) rc |= mat(&w.sh_in, s.n_sh, W) | mat(&w.sh_down, W, s.sff);
@@ -521,7 +521,7 @@ class Zinavik : public Model {
       if (s.shared) {
         MAT(f + "shared.gate", w.sh_in, W, 0, 0, s.sff, W);
         MAT(f + "shared.up", w.sh_in, W, s.sff, 0, s.sff, W);
-        MAT(f + "shared.sg", w.sh_in, W, 2 * static_cast<size_t>(s.sff), 0, 1, W);
+        MAT(f + "shared.sg", w.router, W, s.experts, 0, 1, W);
         MAT(f + "shared.down", w.sh_down, s.sff, 0, 0, W, s.sff);
       }
     }
@@ -551,7 +551,7 @@ class Zinavik : public Model {
       if (!s.mlp) continue;
       F(w.norm2, W, 0.1f, 1.f);
       F(w.hc2.in, ns, 0.1f, 1.0f / ns); F(w.hc2.out, ns, 0.1f, 0.5f); F(w.hc2.mix, static_cast<size_t>(ns) * ns, 0.1f, 1.0f / ns);
-      M(w.router, static_cast<size_t>(s.experts) * W, sw);
+      M(w.router, static_cast<size_t>(s.experts + (s.shared ? 1 : 0)) * W, sw);
       M(w.e_gu, static_cast<size_t>(s.experts) * 2 * s.ff * W, sw);
       M(w.e_down, static_cast<size_t>(s.experts) * W * s.ff, 1.7f / sqrtf(static_cast<float>(s.ff)));
       if (s.shared) { M(w.sh_in, static_cast<size_t>(s.n_sh) * W, sw); M(w.sh_down, static_cast<size_t>(W) * s.sff, 1.7f / sqrtf(static_cast<float>(s.sff))); }
@@ -608,16 +608,17 @@ class Zinavik : public Model {
   int moe(const LayerSpec& s, const LayerWeights& w, int T, int64_t& nl) {
     cudaStream_t st = env.stream;
     int rc = 0;
-    KRN("moe_router", linear(linear_args(h, dt, w.router, dt, scores, DT_F32, T, s.experts, W), st));
-    KRN("moe_route", moe_route(scores, topi, topw, T, s.experts, 1, 1, s.top, st, MOE_SIGMOID));
+    const int nr = s.experts + (s.shared ? 1 : 0);   // router logits and, behind them, the shared expert's gate logit
+    KRN("moe_router", linear(linear_args(h, dt, w.router, dt, scores, DT_F32, T, nr, W), st));
+    KRN("moe_route", moe_route(scores, topi, topw, T, s.experts, 1, 1, s.top, st, MOE_SIGMOID, nr));
     const void* shared_out = nullptr;
-    const void* shared_gate = nullptr;
+    const float* shared_gate = nullptr;
     if (s.shared) {
       KRN("shared_in", project(w.p_shin, w.tc_shin, xm_h, h, w.sh_in, sh, T, s.n_sh, W));
       KRN("glu", glu_clamped(sh, s.n_sh, shact, s.sff, dt, T, s.sff, s.slimit, 1.702f, st));
       KRN("shared_down", project(w.p_shdown, w.tc_shdown, w.xm_shact, shact, w.sh_down, sdown, T, W, s.sff));
       shared_out = sdown;
-      shared_gate = static_cast<const uint8_t*>(sh) + 2 * static_cast<size_t>(s.sff) * dtype_bytes(dt);
+      shared_gate = scores + s.experts;
     }
     const long long gu_stride = 2ll * s.ff * W, down_stride = static_cast<long long>(W) * s.ff;
     static const int moe_tc_min = [] { const char* e = getenv("B200_ZV_MOE_TC_MIN_T"); return e ? atoi(e) : 256; }();   // A/B knob
@@ -634,7 +635,7 @@ class Zinavik : public Model {
       const PickedRows pd = {T * s.top, iota, 1, iota, topi};
       KRN("moe_down", linear_picked_rows(dn, pd, st));
       // pair p of token t is row t * top + k: the combine walks them through an identity table
-      KRN("moe_combine", combine_identity(T, s.top, shared_out, shared_gate, s.n_sh, st));
+      KRN("moe_combine", combine_identity(T, s.top, shared_out, shared_gate, nr, st));
       return rc;
     }
     const int cap = (T * s.top + 63) / 64 * 64 + s.experts * 64;
@@ -669,7 +670,7 @@ class Zinavik : public Model {
         ++nl;
       }
       prof_stop("moe_down");
-      KRN("moe_combine", moe_combine_add(edown16, DT_BF16, pair_pos, nullptr, shared_out, shared_gate, s.n_sh, fo, dt, T, s.top, W, st));
+      KRN("moe_combine", moe_combine_add(edown16, DT_BF16, pair_pos, nullptr, shared_out, shared_gate, nr, fo, dt, T, s.top, W, st));
       return rc;
     }
     LinearArgs up = linear_args(h, dt, w.e_gu, dt, egu, dt, cap, 2 * s.ff, W);
@@ -679,10 +680,10 @@ class Zinavik : public Model {
     LinearArgs dn = linear_args(eact, dt, w.e_down, dt, edown, DT_F32, cap, W, s.ff);
     dn.tile_group = tile_group; dn.wbs = down_stride;
     KRN("moe_down", linear(dn, st));
-    KRN("moe_combine", moe_combine_add(edown, DT_F32, pair_pos, nullptr, shared_out, shared_gate, s.n_sh, fo, dt, T, s.top, W, st));
+    KRN("moe_combine", moe_combine_add(edown, DT_F32, pair_pos, nullptr, shared_out, shared_gate, nr, fo, dt, T, s.top, W, st));
     return rc;
   }
-  int combine_identity(int T, int top, const void* shared_out, const void* shared_gate, int ld_gate, cudaStream_t st) {
+  int combine_identity(int T, int top, const void* shared_out, const float* shared_gate, int ld_gate, cudaStream_t st) {
     return moe_combine_add(edown, DT_F32, iota, nullptr, shared_out, shared_gate, ld_gate, fo, dt, T, top, W, st);
   }
 
