@@ -13,7 +13,7 @@
 // one key for the scores and a slice of the value columns for the output, online softmax in fp32, the warps' partial
 // results meet in shared memory in a fixed order; the sigmoid output gate and the branch scale are applied before the
 // single rounding to the storage type), and `window_attn_mma_kernel` (bf16, head sizes that fit the mma.sync fragments:
-// 128 query rows of one sequence, the heads of one key/value group together, against 64-key tiles on the tensor cores).
+// 64 query rows of one sequence, the heads of one key/value group together, against 64-key tiles on the tensor cores).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <float.h>
@@ -217,10 +217,11 @@ __global__ void __launch_bounds__(kWarpsDecode * 32) window_attn_kernel(WindowAt
 }
 
 // ---------------------------------------------------------------------------------------------- attention on the tensor cores
-// bf16 cache, dim % 16 == 0, vdim % 16 == 0, both <= 128.  A CTA of eight warps owns 128 query rows of one sequence: TQ = 128 / gs
-// consecutive tokens times the gs query heads that share one key/value head (gs = heads / kv_heads when that divides 128,
+// bf16 cache, dim % 16 == 0, vdim % 16 == 0, both <= 128.  A CTA of four warps owns 64 query rows of one sequence: TQ = 64 / gs
+// consecutive tokens times the gs query heads that share one key/value head (gs = heads / kv_heads when that divides 64,
 // else 1 and every query head is its own group), so one key/value tile in shared memory serves the whole group.  Keys
-// come in tiles of 64 from the pages by cp.async, two buffers; first the kept first tokens that lie before the tile's
+// come in tiles of 64 from the pages by cp.async (one buffer: three CTAs per SM hide the copy better than a second buffer
+// per CTA did); first the kept first tokens that lie before the tile's
 // lowest window, then the window itself.  S = Q K^T and O += P V are mma.sync m16n8k16 products with fp32 accumulators;
 // the mask (j <= p, p - j < window or j < keep_first, per row), the scale and the online softmax work on the score
 // fragments in registers (fp32; the exponentials are the fast fp32 intrinsic, as bf16 serving allows), a row's four lanes share
@@ -248,24 +249,24 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-constexpr int kTileRows = 128, kTileKeys = 64, kMmaThreads = 2 * kTileRows, kMmaCtasPerSm = 1;
+constexpr int kTileRows = 64, kTileKeys = 64, kMmaThreads = 2 * kTileRows, kMmaCtasPerSm = 3, kStages = 1;
 constexpr float kMasked = -1e30f;
 
 template <int NV>   // value n-tiles of 8 columns held per thread: vdim <= 8 * NV
 __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_kernel(WindowAttnArgs a, int gs, int TQ, int page_shift) {
   extern __shared__ __align__(16) unsigned char smraw[];
-  __shared__ long long rowoff[2][kTileKeys];                // cache row (in elements) of every key of a tile, looked up once
+  __shared__ long long rowoff[kStages][kTileKeys];                // cache row (in elements) of every key of a tile, looked up once
   const int D = a.dim, Dv = a.vdim, LDK = D + 8, LDV = Dv + 8;
-  bf16* Qs = reinterpret_cast<bf16*>(smraw);                 // [128][LDK]
-  bf16* Ks = Qs + kTileRows * LDK;                           // [2][64][LDK]
-  bf16* Vs = Ks + 2 * kTileKeys * LDK;                       // [2][64][LDV]
+  bf16* Qs = reinterpret_cast<bf16*>(smraw);                 // [rows][LDK]
+  bf16* Ks = Qs + kTileRows * LDK;                           // [stages][64][LDK]
+  bf16* Vs = Ks + kStages * kTileKeys * LDK;                 // [stages][64][LDV]
   const int tid = threadIdx.x, lane = tid & 31, wrp = tid >> 5, g = lane >> 2, t4 = lane & 3;
   // which sequence and which tile of it
   int tile = blockIdx.x, s = 0, n = 0;
   for (; s < a.nseq; ++s) {
     n = a.seqs[s * 8 + 1];
     const int nt = (n + TQ - 1) / TQ;
-    if (tile < nt) break;
+    if (tile < nt) { tile = nt - 1 - tile; break; }   // a sequence's last tiles see the most keys: they start first
     tile -= nt;
   }
   if (s >= a.nseq) return;
@@ -277,7 +278,7 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
   const long long crow = static_cast<long long>(a.kv_heads) * (D + Dv);
   const bf16* cache = static_cast<const bf16*>(a.cache);
   const long long koff = static_cast<long long>(kvh) * D, voff = static_cast<long long>(a.kv_heads) * D + static_cast<long long>(kvh) * Dv;
-  // queries -> bf16 rows (row r: token r / gs, head hy * gs + r % gs); a warp takes rows wrp, wrp + 8, ...
+  // queries -> bf16 rows (row r: token r / gs, head hy * gs + r % gs); a warp takes rows wrp, wrp + warps, ...
   for (int r = wrp; r < kTileRows; r += kMmaThreads / 32) {
     const int tq = r / gs, hh = r - tq * gs;
     const float* src = a.qn + (static_cast<long long>(tok0 + tq) * a.heads + hy * gs + hh) * D;
@@ -304,16 +305,16 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
       const int j = j0 + min(tid, cnt - 1);    // rows past the range repeat its last key: finite values under a zero weight
       const long long slot = page_shift >= 0 ? (static_cast<long long>(bt[j >> page_shift]) << page_shift) + (j & ((1 << page_shift) - 1))
                                              : static_cast<long long>(bt[j / a.page]) * a.page + j % a.page;
-      rowoff[i & 1][tid] = slot * crow;
+      rowoff[i % kStages][tid] = slot * crow;
     }
   };
   // the (row, piece) this thread copies first and its step from one of its pieces to the next: no division per tile
   const int r_first = tid / chunks, c_first = tid - r_first * chunks;
   const int r_step = kMmaThreads / chunks, c_step = kMmaThreads - r_step * chunks;
   auto load_tile = [&](int i) {
-    bf16* kd = Ks + (i & 1) * kTileKeys * LDK;
-    bf16* vd = Vs + (i & 1) * kTileKeys * LDV;
-    const long long* ro = rowoff[i & 1];
+    bf16* kd = Ks + (i % kStages) * kTileKeys * LDK;
+    bf16* vd = Vs + (i % kStages) * kTileKeys * LDV;
+    const long long* ro = rowoff[i % kStages];
     int r = r_first, c = c_first;
     while (r < kTileKeys) {
       const bf16* src = cache + ro[r];
@@ -344,17 +345,17 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
   const bool warp_ok = (16 * wrp + 15) / gs < ntq;
   load_tile(0);
   cp_async_commit();
-  lookup_rows(1);
+  if (kStages == 2) lookup_rows(1);
   __syncthreads();
   for (int i = 0; i < ntiles; ++i) {
-    if (i + 1 < ntiles) { load_tile(i + 1); cp_async_commit(); cp_async_wait<1>(); }
+    if (kStages == 2 && i + 1 < ntiles) { load_tile(i + 1); cp_async_commit(); cp_async_wait<1>(); }
     else cp_async_wait<0>();
     __syncthreads();
-    lookup_rows(i + 2);      // its buffer held tile i's rows, which were consumed when tile i was issued
+    lookup_rows(i + kStages);      // its buffer held tile i's rows, which were consumed when tile i was issued
     int j0, cnt;
     tile_range(i, &j0, &cnt);
-    const bf16* kt = Ks + (i & 1) * kTileKeys * LDK;
-    const bf16* vt = Vs + (i & 1) * kTileKeys * LDV;
+    const bf16* kt = Ks + (i % kStages) * kTileKeys * LDK;
+    const bf16* vt = Vs + (i % kStages) * kTileKeys * LDV;
     float sc[8][4];
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
@@ -434,6 +435,7 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
       }
     }
     __syncthreads();   // the buffer is free for the tile after next
+    if (kStages == 1 && i + 1 < ntiles) { load_tile(i + 1); cp_async_commit(); }
   }
   // finish: row sums over the four lanes of a row, gate, branch scale, one rounding
   const bf16* gate = static_cast<const bf16*>(a.gate);
@@ -519,14 +521,16 @@ int window_attention(const WindowAttnArgs& a, cudaStream_t st) {
     const int TQ = kTileRows / gs;
     int page_shift = -1;
     for (int b = 0; b < 31; ++b) if ((1 << b) == a.page) page_shift = b;
-    const size_t smem = (static_cast<size_t>(kTileRows + 2 * kTileKeys) * (a.dim + 8) + 2 * static_cast<size_t>(kTileKeys) * (a.vdim + 8)) * sizeof(bf16);
+    const size_t smem = (static_cast<size_t>(kTileRows + kStages * kTileKeys) * (a.dim + 8) + kStages * static_cast<size_t>(kTileKeys) * (a.vdim + 8)) * sizeof(bf16);
     dim3 grid(static_cast<unsigned>((a.T + TQ - 1) / TQ + a.nseq), static_cast<unsigned>(a.heads / gs));
     static std::atomic<unsigned long long> set8{0}, set16{0};
     if (a.vdim <= 64) {
       if (!ensure_dynamic_smem(window_attn_mma_kernel<8>, 112 * 1024, &set8)) return -2;
+      cudaFuncSetAttribute(window_attn_mma_kernel<8>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
       window_attn_mma_kernel<8><<<grid, kMmaThreads, smem, st>>>(a, gs, TQ, page_shift);
     } else {
       if (!ensure_dynamic_smem(window_attn_mma_kernel<16>, 112 * 1024, &set16)) return -2;
+      cudaFuncSetAttribute(window_attn_mma_kernel<16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
       window_attn_mma_kernel<16><<<grid, kMmaThreads, smem, st>>>(a, gs, TQ, page_shift);
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
