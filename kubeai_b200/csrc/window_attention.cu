@@ -220,8 +220,9 @@ __global__ void __launch_bounds__(kWarpsDecode * 32) window_attn_kernel(WindowAt
 // bf16 cache, dim % 16 == 0, vdim % 16 == 0, both <= 128.  A CTA of four warps owns 64 query rows of one sequence: TQ = 64 / gs
 // consecutive tokens times the gs query heads that share one key/value head (gs = heads / kv_heads when that divides 64,
 // else 1 and every query head is its own group), so one key/value tile in shared memory serves the whole group.  Keys
-// come in tiles of 64 from the pages by cp.async (one buffer: three CTAs per SM hide the copy better than a second buffer
-// per CTA did); first the kept first tokens that lie before the tile's
+// come in tiles of 64 from the pages by cp.async into one key and one value buffer (three CTAs fit an SM): the next keys
+// are copied under the softmax and the second product, the next values under the next scores; first come the kept first
+// tokens that lie before the tile's
 // lowest window, then the window itself.  S = Q K^T and O += P V are mma.sync m16n8k16 products with fp32 accumulators;
 // the mask (j <= p, p - j < window or j < keep_first, per row), the scale and the online softmax work on the score
 // fragments in registers (fp32; the exponentials are the fast fp32 intrinsic, as bf16 serving allows), a row's four lanes share
@@ -249,17 +250,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-constexpr int kTileRows = 64, kTileKeys = 64, kMmaThreads = 2 * kTileRows, kMmaCtasPerSm = 3, kStages = 1;
+constexpr int kTileRows = 64, kTileKeys = 64, kMmaThreads = 2 * kTileRows, kMmaCtasPerSm = 3;
 constexpr float kMasked = -1e30f;
 
 template <int NV>   // value n-tiles of 8 columns held per thread: vdim <= 8 * NV
 __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_kernel(WindowAttnArgs a, int gs, int TQ, int page_shift) {
   extern __shared__ __align__(16) unsigned char smraw[];
-  __shared__ long long rowoff[kStages][kTileKeys];                // cache row (in elements) of every key of a tile, looked up once
+  __shared__ long long rowoff[kTileKeys];                // cache row (in elements) of every key of a tile, looked up once
   const int D = a.dim, Dv = a.vdim, LDK = D + 8, LDV = Dv + 8;
   bf16* Qs = reinterpret_cast<bf16*>(smraw);                 // [rows][LDK]
-  bf16* Ks = Qs + kTileRows * LDK;                           // [stages][64][LDK]
-  bf16* Vs = Ks + kStages * kTileKeys * LDK;                 // [stages][64][LDV]
+  bf16* Ks = Qs + kTileRows * LDK;                           // [64][LDK]
+  bf16* Vs = Ks + kTileKeys * LDK;                           // [64][LDV]
   const int tid = threadIdx.x, lane = tid & 31, wrp = tid >> 5, g = lane >> 2, t4 = lane & 3;
   // which sequence and which tile of it
   int tile = blockIdx.x, s = 0, n = 0;
@@ -305,24 +306,31 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
       const int j = j0 + min(tid, cnt - 1);    // rows past the range repeat its last key: finite values under a zero weight
       const long long slot = page_shift >= 0 ? (static_cast<long long>(bt[j >> page_shift]) << page_shift) + (j & ((1 << page_shift) - 1))
                                              : static_cast<long long>(bt[j / a.page]) * a.page + j % a.page;
-      rowoff[i % kStages][tid] = slot * crow;
+      rowoff[tid] = slot * crow;
     }
   };
-  // the (row, piece) this thread copies first and its step from one of its pieces to the next: no division per tile
-  const int r_first = tid / chunks, c_first = tid - r_first * chunks;
-  const int r_step = kMmaThreads / chunks, c_step = kMmaThreads - r_step * chunks;
-  auto load_tile = [&](int i) {
-    bf16* kd = Ks + (i % kStages) * kTileKeys * LDK;
-    bf16* vd = Vs + (i % kStages) * kTileKeys * LDV;
-    const long long* ro = rowoff[i % kStages];
-    int r = r_first, c = c_first;
+  // Keys and values of a tile are copied separately (the key buffer is free again after the scores, the value buffer after
+  // the second product).  The (row, piece) a thread copies first and its step to its next piece: no division per tile.
+  const int vchunks = chunks - kchunks;
+  const int kr_first = tid / kchunks, kc_first = tid - kr_first * kchunks, kr_step = kMmaThreads / kchunks, kc_step = kMmaThreads - kr_step * kchunks;
+  const int vr_first = tid / vchunks, vc_first = tid - vr_first * vchunks, vr_step = kMmaThreads / vchunks, vc_step = kMmaThreads - vr_step * vchunks;
+  auto load_keys = [&]() {
+    int r = kr_first, c = kc_first;
     while (r < kTileKeys) {
-      const bf16* src = cache + ro[r];
-      if (c < kchunks) cp_async16(smem_u32(kd + r * LDK + c * 8), src + koff + c * 8);
-      else cp_async16(smem_u32(vd + r * LDV + (c - kchunks) * 8), src + voff + (c - kchunks) * 8);
-      r += r_step; c += c_step;
-      if (c >= chunks) { c -= chunks; ++r; }
+      cp_async16(smem_u32(Ks + r * LDK + c * 8), cache + rowoff[r] + koff + c * 8);
+      r += kr_step; c += kc_step;
+      if (c >= kchunks) { c -= kchunks; ++r; }
     }
+    cp_async_commit();
+  };
+  auto load_values = [&]() {
+    int r = vr_first, c = vc_first;
+    while (r < kTileKeys) {
+      cp_async16(smem_u32(Vs + r * LDV + c * 8), cache + rowoff[r] + voff + c * 8);
+      r += vr_step; c += vc_step;
+      if (c >= vchunks) { c -= vchunks; ++r; }
+    }
+    cp_async_commit();
   };
   float m[2] = {kMasked, kMasked}, l[2] = {0.f, 0.f};
   float o[NV][4];
@@ -343,19 +351,16 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
   // the positions of the warp's 16 rows, for the whole-tile test
   const int warp_pmin = p0 + (16 * wrp) / gs, warp_pmax = p0 + (16 * wrp + 15) / gs;
   const bool warp_ok = (16 * wrp + 15) / gs < ntq;
-  load_tile(0);
-  cp_async_commit();
-  if (kStages == 2) lookup_rows(1);
-  __syncthreads();
+  load_keys();
+  load_values();
   for (int i = 0; i < ntiles; ++i) {
-    if (kStages == 2 && i + 1 < ntiles) { load_tile(i + 1); cp_async_commit(); cp_async_wait<1>(); }
-    else cp_async_wait<0>();
+    cp_async_wait<1>();        // this tile's keys have landed (its values may still be on their way)
     __syncthreads();
-    lookup_rows(i + kStages);      // its buffer held tile i's rows, which were consumed when tile i was issued
+    lookup_rows(i + 1);        // every copy of tile i has been issued: the row table is free for the next tile
     int j0, cnt;
     tile_range(i, &j0, &cnt);
-    const bf16* kt = Ks + (i % kStages) * kTileKeys * LDK;
-    const bf16* vt = Vs + (i % kStages) * kTileKeys * LDV;
+    const bf16* kt = Ks;
+    const bf16* vt = Vs;
     float sc[8][4];
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
@@ -370,6 +375,9 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
         mma_bf16(sc[2 * nb + 1], af, bfr[2], bfr[3]);
       }
     }
+    __syncthreads();           // the key buffer is free, the next tile's row table is written
+    const bool more = i + 1 < ntiles;
+    if (more) load_keys();     // the next keys arrive under the softmax and the second product
     // mask, scale, running maximum.  A tile that every row of the warp sees whole (all keys at or before the warp's
     // first position and inside its last row's window) needs no per-element test.
     float mx[2] = {kMasked, kMasked};
@@ -417,6 +425,8 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
 #pragma unroll
     for (int i2 = 0; i2 < NV; ++i2) { o[i2][0] *= corr[0]; o[i2][1] *= corr[0]; o[i2][2] *= corr[1]; o[i2][3] *= corr[1]; }
     // O += P V
+    if (more) cp_async_wait<1>(); else cp_async_wait<0>();     // this tile's values
+    __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
       uint32_t pf[4];
@@ -434,8 +444,9 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
         }
       }
     }
-    __syncthreads();   // the buffer is free for the tile after next
-    if (kStages == 1 && i + 1 < ntiles) { load_tile(i + 1); cp_async_commit(); }
+    __syncthreads();           // the value buffer is free
+    if (more) load_values();   // the next values arrive under the next tile's scores
+    else cp_async_commit();    // keeps the count of groups in flight the same on the last round
   }
   // finish: row sums over the four lanes of a row, gate, branch scale, one rounding
   const bf16* gate = static_cast<const bf16*>(a.gate);
@@ -521,7 +532,7 @@ int window_attention(const WindowAttnArgs& a, cudaStream_t st) {
     const int TQ = kTileRows / gs;
     int page_shift = -1;
     for (int b = 0; b < 31; ++b) if ((1 << b) == a.page) page_shift = b;
-    const size_t smem = (static_cast<size_t>(kTileRows + kStages * kTileKeys) * (a.dim + 8) + kStages * static_cast<size_t>(kTileKeys) * (a.vdim + 8)) * sizeof(bf16);
+    const size_t smem = (static_cast<size_t>(kTileRows + kTileKeys) * (a.dim + 8) + static_cast<size_t>(kTileKeys) * (a.vdim + 8)) * sizeof(bf16);
     dim3 grid(static_cast<unsigned>((a.T + TQ - 1) / TQ + a.nseq), static_cast<unsigned>(a.heads / gs));
     static std::atomic<unsigned long long> set8{0}, set16{0};
     if (a.vdim <= 64) {
