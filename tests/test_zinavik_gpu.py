@@ -174,6 +174,42 @@ def test_bfloat16_tensor_core_attention_equals_the_general_kernel(tmp_path, monk
         assert np.median(rel_err(a, b.astype(np.float64))) < 0.012 and rel_err(a, b.astype(np.float64)).max() < 0.05
 
 
+def test_bfloat16_mixed_batches_on_the_tensor_core_kernel_equal_each_request_alone(tmp_path, monkeypatch):
+    """Portions of several prompts beside single decoded tokens in one step, head sizes that take the tensor-core kernel:
+    a sequence that brings one token is a tile of one row, a portion may start in the middle of a page or a key tile."""
+    layers = [layer(l=left(heads=4, kv_heads=2, dim=32, vdim=16, window=40, keep_first=6, rot_dims=16, scale=0.35), mlp=moe(experts=3, top=3, ff=16, shared=16))
+              for _ in range(2)]
+    cfg, W, d = build(tmp_path, layers, seed=71, width=32)
+    o = oracle_for(cfg, W)
+    seqs = [toks(n, cfg["vocab"], 72 + i) for i, n in enumerate((150, 61, 9, 120))]
+    plan = [(70, 1, 9, 33), (37, 1, 0, 2), (1, 40, 0, 64), (42, 1, 0, 1), (0, 18, 0, 20)]
+    monkeypatch.setenv("B200_WATTN_MMA", "1")
+    with open_engine(d, dtype="bfloat16", max_tokens=160) as e:
+        rids = [e.feed_open() for _ in seqs]
+        at, got, step = [0] * 4, [[] for _ in seqs], 0
+        while any(at[i] < len(seqs[i]) for i in range(4)):
+            entries, idx = [], []
+            for i in range(4):
+                n = min(plan[min(step, len(plan) - 1)][i] or (1 if step >= len(plan) else 0), len(seqs[i]) - at[i])
+                if n > 0:
+                    entries.append((rids[i], seqs[i][at[i]:at[i] + n], list(range(n))))
+                    idx.append((i, n))
+            out = e.feed_step(entries)
+            r = 0
+            for i, n in idx:
+                got[i].append(out[r:r + n])
+                at[i] += n
+                r += n
+            step += 1
+        for r in rids:
+            e.feed_close(r)
+        alone = [feed_whole(e, t) for t in seqs]
+    for i in range(4):
+        g = np.concatenate(got[i])
+        close16(g, o.forward(seqs[i]))
+        assert np.median(rel_err(g, alone[i].astype(np.float64))) < 0.012 and rel_err(g, alone[i].astype(np.float64)).max() < 0.06
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_medium_sizes_on_every_projection_path(tmp_path, dtype):
     layers = [layer(l=left(heads=4, kv_heads=2, dim=16, vdim=24, window=33, keep_first=5), r=right(heads=2, dim=16, vdim=24),
