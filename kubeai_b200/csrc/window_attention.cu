@@ -351,6 +351,11 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
   // the positions of the warp's 16 rows, for the whole-tile test
   const int warp_pmin = p0 + (16 * wrp) / gs, warp_pmax = p0 + (16 * wrp + 15) / gs;
   const bool warp_ok = (16 * wrp + 15) / gs < ntq;
+  // shared-memory addresses of this lane's ldmatrix rows, formed once: the loops below only add multiples of a k-step
+  const uint32_t q_base = smem_u32(Qs + (16 * wrp + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + (lane >> 4) * 8);
+  const uint32_t k_base = smem_u32(Ks + ((lane & 7) + (lane >> 4) * 8) * LDK + ((lane >> 3) & 1) * 8);
+  const uint32_t v_base = smem_u32(Vs + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDV + (lane >> 4) * 8);
+  const uint32_t k_blk = 16 * LDK * sizeof(bf16), v_blk = 16 * LDV * sizeof(bf16);
   load_keys();
   load_values();
   for (int i = 0; i < ntiles; ++i) {
@@ -359,18 +364,17 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
     lookup_rows(i + 1);        // every copy of tile i has been issued: the row table is free for the next tile
     int j0, cnt;
     tile_range(i, &j0, &cnt);
-    const bf16* kt = Ks;
-    const bf16* vt = Vs;
     float sc[8][4];
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
-    for (int ks = 0; ks < D; ks += 16) {
+#pragma unroll 2
+    for (int ks = 0; ks < 2 * D; ks += 32) {      // byte offset of the k-step
       uint32_t af[4];
-      ldsm_x4(af, smem_u32(Qs + (16 * wrp + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + ks + (lane >> 4) * 8));
+      ldsm_x4(af, q_base + ks);
 #pragma unroll
       for (int nb = 0; nb < 4; ++nb) {
         uint32_t bfr[4];
-        ldsm_x4(bfr, smem_u32(kt + (16 * nb + (lane & 7) + (lane >> 4) * 8) * LDK + ks + ((lane >> 3) & 1) * 8));
+        ldsm_x4(bfr, k_base + nb * k_blk + ks);
         mma_bf16(sc[2 * nb], af, bfr[0], bfr[1]);
         mma_bf16(sc[2 * nb + 1], af, bfr[2], bfr[3]);
       }
@@ -438,7 +442,7 @@ __global__ void __launch_bounds__(kMmaThreads, kMmaCtasPerSm) window_attn_mma_ke
       for (int nb = 0; nb < NV / 2; ++nb) {
         if (2 * nb < nv) {
           uint32_t bfr[4];
-          ldsm_x4_trans(bfr, smem_u32(vt + (16 * kk + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + 16 * nb + (lane >> 4) * 8));
+          ldsm_x4_trans(bfr, v_base + kk * v_blk + nb * 32);
           mma_bf16(o[2 * nb], pf, bfr[0], bfr[1]);
           mma_bf16(o[2 * nb + 1], pf, bfr[2], bfr[3]);
         }
