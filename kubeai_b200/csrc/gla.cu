@@ -52,7 +52,8 @@ __global__ void gla_decay_kernel(float* z, const float* bias, int HD, float inv_
 // from shared memory then feeds twice the arithmetic).  Threads of a warp share one row slice (part = thread / tcols), so a
 // shared-memory read of q, k or alpha is one broadcast; the P partial outputs of a column meet in shared memory and are
 // summed by the pass that writes the round's outputs.
-template <typename T, int NC>
+// CD: one constant decay per head (GlaArgs::head_decay): no decay row is staged or read, the constant sits in a register.
+template <typename T, int NC, bool CD>
 __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, int rpp, int G) {
   extern __shared__ __align__(16) float sm[];
   const int seq = blockIdx.z, head = blockIdx.y;
@@ -80,7 +81,7 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
     }
   const int slice_elems = P * rpp;
   const bool silu = a.act == GLA_ACT_SILU;
-  const float hdecay = a.head_decay ? a.head_decay[head] : 0.f;   // one constant per head instead of per-channel decays
+  const float hdecay = CD ? a.head_decay[head] : 0.f;
   for (int g0 = 0; g0 < n; g0 += G) {
     const int gn = min(G, n - g0);
     __syncthreads();
@@ -98,7 +99,7 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
           if (silu) { qv = siluf_(qv); kv = siluf_(kv); }
           s3[(tt * 3) * Dp] = qv * a.q_scale;
           s3[(tt * 3 + 1) * Dp] = kv;
-          s3[(tt * 3 + 2) * Dp] = a.head_decay ? hdecay : __ldg(a.z + row * (a.heads * D) + c);
+          if (!CD) s3[(tt * 3 + 2) * Dp] = __ldg(a.z + row * (a.heads * D) + c);
         }
       } else {
         for (int tt = 0; tt < gn; ++tt) { s3[(tt * 3) * Dp] = 0.f; s3[(tt * 3 + 1) * Dp] = 0.f; s3[(tt * 3 + 2) * Dp] = 0.f; }
@@ -121,7 +122,7 @@ __global__ void __launch_bounds__(kThreads) gla_scan_kernel(GlaArgs a, int P, in
 #pragma unroll
       for (int m = 0; m < kRows / 4; ++m) {
         if (4 * m < rpp) {
-          const float4 qa = q4[m], ka = k4[m], aa = a4[m];
+          const float4 qa = q4[m], ka = k4[m], aa = CD ? make_float4(hdecay, hdecay, hdecay, hdecay) : a4[m];
 #pragma unroll
           for (int c = 0; c < NC; ++c) {
             float* Sc = S[c] + 4 * m;
@@ -249,13 +250,14 @@ int gla_scan(const GlaArgs& a, cudaStream_t st) {
     const long long total = static_cast<long long>(a.T) * a.heads * a.dim;
     if (total > 0) gla_decay_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(a.z, a.z_bias, a.heads * a.dim, a.inv_tau, total);
   }
+#define SCAN(T_, NC_) do { if (a.head_decay) gla_scan_kernel<T_, NC_, true><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G); \
+                          else gla_scan_kernel<T_, NC_, false><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G); } while (0)
   if (a.t == DT_BF16) {
-    if (NC == 2) gla_scan_kernel<bf16, 2><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G);
-    else gla_scan_kernel<bf16, 1><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G);
+    if (NC == 2) SCAN(bf16, 2); else SCAN(bf16, 1);
   } else {
-    if (NC == 2) gla_scan_kernel<float, 2><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G);
-    else gla_scan_kernel<float, 1><<<grid, kThreads, smem, st>>>(a, P, rows_per_part, G);
+    if (NC == 2) SCAN(float, 2); else SCAN(float, 1);
   }
+#undef SCAN
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
