@@ -81,6 +81,7 @@ def mix_wide(tmp_path_factory):
     ("loop_in_the_middle", [layer(), layer(mlp=None), layer()], dict(loop=(1, 2, 3))),
     ("loop_over_everything_once", [layer(), layer()], dict(loop=(0, 2, 1))),
     ("odd_width", [layer(), layer()], dict(width=21, vocab=33)),
+    ("large_eps_in_every_norm", [layer(), layer()], dict(eps=0.05, emb_scale=0.5)),
 ])
 def test_each_mechanism_matches_the_oracle(tmp_path, name, layers, kw):
     cfg, W, d = build(tmp_path, layers, seed=3, **kw)
