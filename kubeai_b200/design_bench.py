@@ -37,7 +37,7 @@ def nomanex_config(z):
 def zinavik_config(z):
     H = z["heads"]
     lf = dict(heads=H, kv_heads=max(1, H // 4), dim=DIM, vdim=VDIM, mask=dict(size=z["window"], keep_first=4),
-              rot=dict(base=10000.0, dims=ROT, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0)), scale=DIM ** -0.5)
+              rot=dict(base=10000.0, dims=ROT, scaling=dict(factor=4.0, original=2048, fast=32.0, slow=1.0)), scale=DIM ** -0.5)
     rt = dict(heads=H, dim=DIM, vdim=VDIM, decay=[1.0 - 2.0 ** -(5.0 + 5.0 * h / max(H - 1, 1)) for h in range(H)])
     mo = dict(kind="moe", expert=dict(ff=z["eff"], limit=7.0), router=dict(experts=z["experts"], top=z["top"]),
               shared=dict(ff=z["eff"], limit=7.0))
